@@ -642,7 +642,8 @@ static Json dispatch(const std::string &method, const Json &a, Json *error_detai
             kv.push_back(s.is_object() ? KVSpec{(int)s.get("num_kv_heads").as_int(), (int)s.get("head_dim").as_int(),
                                                 (int)s.get("window").as_int(),
                                                 s.has("v_head_dim") ? (int)s.get("v_head_dim").as_int() : 0,
-                                                s.has("values_in_keys") && s.get("values_in_keys").as_bool()}
+                                                s.has("values_in_keys") && s.get("values_in_keys").as_bool(),
+                                                s.has("keep_first") ? (int)s.get("keep_first").as_int() : 0}
                                        : KVSpec());
         std::vector<StateSpec> st;
         for (auto &s : a.get("state_specs").items()) {

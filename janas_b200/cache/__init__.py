@@ -45,10 +45,12 @@ class KVSpec:
     window: int = 0
     v_head_dim: int = 0
     values_in_keys: bool = False
+    keep_first: int = 0     # with a window: the first positions stay readable for the whole sequence
 
     def to_json(self):
         return {"num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim, "window": self.window,
-                "v_head_dim": self.v_head_dim, "values_in_keys": self.values_in_keys}
+                "v_head_dim": self.v_head_dim, "values_in_keys": self.values_in_keys,
+                "keep_first": self.keep_first}
 
 
 @dataclass(frozen=True)
@@ -168,7 +170,8 @@ class KVGroup:
         self.index_in_cache = index
         v = info.get("v_head_dim", 0)
         self.spec = KVSpec(info["num_kv_heads"], info["head_dim"], info["window"],
-                           0 if v == info["head_dim"] else v, bool(info.get("values_in_keys", False)))
+                           0 if v == info["head_dim"] else v, bool(info.get("values_in_keys", False)),
+                           int(info.get("keep_first", 0)))
         self.entries: List[int] = list(info["entries"])
         self.index = {e: i for i, e in enumerate(self.entries)}
         self.pool = _GroupPool(self)

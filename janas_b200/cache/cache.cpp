@@ -113,7 +113,8 @@ void KVGroup::release_unseen(int slot, long long next_pos) {
     auto &have = pages[(size_t)slot];
     int first = std::min(first_needed_page(next_pos), (int)have.size());
     std::vector<int> gone;
-    for (int i = 0; i < first; i++)
+    // the pages of the kept first positions stay
+    for (int i = (int)pages_for(spec.keep_first); i < first; i++)
         if (have[(size_t)i] >= 0) { gone.push_back(have[(size_t)i]); have[(size_t)i] = -1; }
     if (!gone.empty()) pool.give_back(gone);
 }
@@ -133,7 +134,8 @@ int KVGroup::held(int slot) const {
 
 // ------------------------------------------------------------------- cache
 Cache::Cache(const std::vector<KVSpec> &kv_specs, const std::vector<StateSpec> &state_specs,
-             long long max_tok, int max_sq, DType dt, Device *device)
+             long long max_tok, int max_sq, DType dt, Device *device,
+             const std::vector<StateSpec> &block_state_specs)
     : dev(device), dtype(dt), max_tokens(pages_for(max_tok) * PAGE), max_seqs(max_sq),
       slots(max_sq > 0 ? max_sq : 1) {
     if (max_tok <= 0 || max_sq <= 0) fail(JB_LLM_EINVAL, "max_tokens and max_seqs must be positive");
@@ -177,6 +179,8 @@ Cache::Cache(const std::vector<KVSpec> &kv_specs, const std::vector<StateSpec> &
     }
     for (size_t e = 0; e < state_specs.size(); e++)
         if (!state_specs[e].none()) state_spec[(int)e] = state_specs[e];
+    for (size_t e = 0; e < block_state_specs.size(); e++)
+        if (!block_state_specs[e].none()) block_state_spec[(int)e] = block_state_specs[e];
     if (dev) {
         rng = dev->tensor(I64, {max_sq}, true);
         temperature = dev->tensor(F32, {max_sq}, true);
@@ -188,6 +192,11 @@ Cache::Cache(const std::vector<KVSpec> &kv_specs, const std::vector<StateSpec> &
             shape.insert(shape.end(), kv.second.shape.begin(), kv.second.shape.end());
             mixer_state[kv.first] = dev->tensor(kv.second.dtype, shape, true);
         }
+        for (auto &kv : block_state_spec) {
+            std::vector<long long> shape = {max_sq};
+            shape.insert(shape.end(), kv.second.shape.begin(), kv.second.shape.end());
+            block_state[kv.first] = dev->tensor(kv.second.dtype, shape, true);
+        }
     }
 }
 
@@ -195,6 +204,11 @@ void Cache::zero_state(int slot) {
     if (!dev) return;
     for (auto &kv : mixer_state) {
         size_t b = state_spec[kv.first].bytes();
+        cuda_check(cudaMemsetAsync((char *)kv.second.ptr + (size_t)slot * b, 0, b, dev->stream),
+                   "clearing a sequence's state");
+    }
+    for (auto &kv : block_state) {
+        size_t b = block_state_spec[kv.first].bytes();
         cuda_check(cudaMemsetAsync((char *)kv.second.ptr + (size_t)slot * b, 0, b, dev->stream),
                    "clearing a sequence's state");
     }
@@ -224,10 +238,12 @@ void Cache::free_sequence(int slot) {
 bool Cache::can_truncate(int slot, long long n) const {
     if (!slots.live(slot) || n < 0 || n > length_[(size_t)slot]) return false;
     if (n == 0 || n == length_[(size_t)slot]) return true;
-    if (!state_spec.empty()) return false;
+    if (!state_spec.empty() || !block_state_spec.empty()) return false;
     for (auto &g : groups) {
         auto &have = g->pages[(size_t)slot];
         for (long long i = g->first_needed_page(n); i < pages_for(n); i++)
+            if (have[(size_t)i] < 0) return false;
+        for (long long i = 0; i < std::min(pages_for(g->spec.window ? g->spec.keep_first : 0), pages_for(n)); i++)
             if (have[(size_t)i] < 0) return false;
     }
     return true;
@@ -399,6 +415,7 @@ Json Cache::describe() const {
         j.set("v_head_dim", g->spec.value_dim());
         j.set("values_in_keys", g->spec.values_in_keys);
         j.set("window", g->spec.window);
+        j.set("keep_first", g->spec.window ? g->spec.keep_first : 0);
         Json es = Json::array();
         for (int e : g->entries) es.push(e);
         j.set("entries", es);
@@ -415,6 +432,9 @@ Json Cache::describe() const {
     Json st = Json::array();
     for (auto &kv : state_spec) st.push(kv.first);
     o.set("state_entries", st);
+    Json bst = Json::array();
+    for (auto &kv : block_state_spec) bst.push(kv.first);
+    o.set("block_state_entries", bst);
     return o;
 }
 

@@ -91,11 +91,15 @@ struct KVSpec {
     // The values are the first v_head_dim entries of the keys' rows (a latent that is
     // key and value at once): the group then has no V tensor.
     bool values_in_keys = false;
+    // With a window: the first keep_first positions stay readable for the whole sequence
+    // (the pages that hold them are never given back while the sequence lives).
+    int keep_first = 0;
     bool none() const { return num_kv_heads == 0; }
     int value_dim() const { return v_head_dim > 0 ? v_head_dim : head_dim; }
     bool operator==(const KVSpec &o) const {
         return num_kv_heads == o.num_kv_heads && head_dim == o.head_dim && window == o.window &&
-               value_dim() == o.value_dim() && values_in_keys == o.values_in_keys;
+               value_dim() == o.value_dim() && values_in_keys == o.values_in_keys &&
+               (window ? keep_first : 0) == (o.window ? o.keep_first : 0);
     }
 };
 
@@ -149,8 +153,11 @@ public:
     // count rounded up to a multiple of PAGE; max_seqs: the most sequences alive
     // at one time.  dev null: bookkeeping only, no storage (for tests of the
     // decisions on a machine without a GPU).
+    // block_state_specs[e] (may be shorter than the run order, or empty): fixed-size state
+    // that entry e's block arrangement keeps beside its mixer's, zeroed with it.
     Cache(const std::vector<KVSpec> &kv_specs, const std::vector<StateSpec> &state_specs,
-          long long max_tokens, int max_seqs, DType dtype, Device *dev);
+          long long max_tokens, int max_seqs, DType dtype, Device *dev,
+          const std::vector<StateSpec> &block_state_specs = {});
 
     // sequences
     int new_sequence();
@@ -189,6 +196,8 @@ public:
     DevTensor rng, temperature, top_k, top_p, min_p;
     std::map<int, DevTensor> mixer_state;          // entry -> [max_seqs, *shape]
     std::map<int, StateSpec> state_spec;
+    std::map<int, DevTensor> block_state;          // entry -> [max_seqs, *shape]
+    std::map<int, StateSpec> block_state_spec;
 
 private:
     std::vector<long long> length_;

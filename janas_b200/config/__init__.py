@@ -71,7 +71,7 @@ class LayerSpec:
     block: str
     mixer: PartSpec
     feed_forward: Optional[PartSpec]        # None: the layer has no feed-forward (and no ffn_norm)
-    mixer_norm: PartSpec
+    mixer_norm: Optional[PartSpec]          # None: the arrangement's sublayers read the residual stream itself
     ffn_norm: Optional[PartSpec]
     prefix: str
     mixer_name: str = "self_attn"
@@ -94,7 +94,7 @@ class LayerSpec:
         none = {"kind": "", "params": {}}
         d = {"block": self.block, "mixer": self.mixer.to_json(),
              "feed_forward": self.feed_forward.to_json() if self.feed_forward else none,
-             "mixer_norm": self.mixer_norm.to_json(),
+             "mixer_norm": self.mixer_norm.to_json() if self.mixer_norm else none,
              "ffn_norm": self.ffn_norm.to_json() if self.ffn_norm else none,
              "prefix": self.prefix, "mixer_name": self.mixer_name, "ffn_name": self.ffn_name,
              "mixer_norm_name": self.mixer_norm_name, "ffn_norm_name": self.ffn_norm_name,
@@ -115,7 +115,7 @@ class LayerSpec:
             return PartSpec.from_json(v) if v and v.get("kind") else None
         return LayerSpec(
             l["block"], PartSpec.from_json(l["mixer"]), part("feed_forward"),
-            PartSpec.from_json(l["mixer_norm"]), part("ffn_norm"), l["prefix"],
+            part("mixer_norm"), part("ffn_norm"), l["prefix"],
             l["mixer_name"], l["ffn_name"], l["mixer_norm_name"], l["ffn_norm_name"],
             part("post_mixer_norm"), part("post_ffn_norm"),
             l.get("post_mixer_norm_name", "post_mixer_norm"),
@@ -149,6 +149,7 @@ class ModelSpec:
     head_name: str = "lm_head.weight"
     position_table_name: str = ""      # a table of learned position vectors; "": none
     logit_scale: float = 1.0
+    embedding_scale: float = 1.0       # a factor on the embedding rows (a tied head reads the table without it)
     embedding_norm: Optional[PartSpec] = None      # a norm on the embedding rows
     embedding_norm_name: str = "model.embed_norm"
 
@@ -167,6 +168,8 @@ class ModelSpec:
             d["position_table_name"] = self.position_table_name
         if self.logit_scale != 1.0:
             d["logit_scale"] = self.logit_scale
+        if self.embedding_scale != 1.0:
+            d["embedding_scale"] = self.embedding_scale
         if self.embedding_norm:
             d["embedding_norm"] = self.embedding_norm.to_json()
             d["embedding_norm_name"] = self.embedding_norm_name
@@ -178,6 +181,7 @@ class ModelSpec:
         return ModelSpec(
             position_table_name=d.get("position_table_name", ""),
             logit_scale=d.get("logit_scale", 1.0),
+            embedding_scale=d.get("embedding_scale", 1.0),
             embedding_norm=PartSpec.from_json(d["embedding_norm"]) if d.get("embedding_norm") else None,
             embedding_norm_name=d.get("embedding_norm_name", "model.embed_norm"),
             architecture=d["architecture"], hidden_size=d["hidden_size"],
@@ -281,8 +285,41 @@ class DunavikConfig:
         return hash(json.dumps(self.to_dict(), sort_keys=True))
 
 
+@dataclass(frozen=True)
+class KefesunConfig:
+    """The Kefesun decoder's ``config.json`` keys, as the library read them."""
+    vocab: int
+    width: int
+    norm_eps: float
+    embedding_scale: float
+    taps: int                                 # canon.taps; 0: no convolution in front of the sublayers
+    layers: Tuple[Mapping[str, Any], ...]     # each: type, mixer {...}, mlp {...} or None
+    eos_token_ids: Tuple[int, ...] = ()
+    architecture: str = "Kefesun"
+    _json: Mapping[str, Any] = field(default_factory=dict, compare=False, repr=False)
+    _spec: Mapping[str, Any] = field(default_factory=dict, compare=False, repr=False)
+
+    @classmethod
+    def from_dict(cls, d: Mapping[str, Any]) -> "KefesunConfig":
+        return _wrap(_call("config.parse", config=dict(d)))
+
+    def to_dict(self) -> Dict[str, Any]:
+        return dict(self._json)
+
+    def to_model_spec(self) -> ModelSpec:
+        return ModelSpec.from_json(self._spec)
+
+    def __hash__(self) -> int:
+        return hash(json.dumps(self.to_dict(), sort_keys=True))
+
+
 def _wrap(r: Mapping[str, Any]):
     c = r["config"]
+    if r["architecture"] == "Kefesun":
+        return KefesunConfig(
+            vocab=c["vocab"], width=c["width"], norm_eps=c["norm"]["eps"],
+            embedding_scale=c["embedding"]["scale"], taps=(c.get("canon") or {}).get("taps", 0),
+            layers=tuple(c["layers"]), eos_token_ids=tuple(r["eos_token_ids"]), _json=c, _spec=r["spec"])
     if r["architecture"] == "Dunavik":
         return DunavikConfig(
             vocab=c["vocab"], width=c["width"], norm_eps=c["norm"]["eps"],
@@ -323,4 +360,4 @@ def config_from_dir(model_dir: str):
 
 
 __all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config",
-           "ZuzelornConfig", "DunavikConfig", "config_from_dict", "config_from_dir", "known_architectures"]
+           "ZuzelornConfig", "DunavikConfig", "KefesunConfig", "config_from_dict", "config_from_dir", "known_architectures"]

@@ -36,6 +36,7 @@ static Tables &ready() {
         register_qwen3();
         register_zuzelorn();
         register_dunavik();
+        register_kefesun();
     });
     return raw_tables();
 }

@@ -37,9 +37,10 @@ std::string architecture_name(const Json &config_json);
 std::unique_ptr<ArchConfig> config_from_json(const Json &config_json);
 std::unique_ptr<ArchConfig> config_from_dir(const std::string &model_dir);
 
-// defined in qwen3.cpp, zuzelorn.cpp and dunavik.cpp; called once by the registry
+// defined in qwen3.cpp, zuzelorn.cpp, dunavik.cpp and kefesun.cpp; called once by the registry
 void register_qwen3();
 void register_zuzelorn();
 void register_dunavik();
+void register_kefesun();
 
 }  // namespace jb

@@ -111,6 +111,7 @@ Json ModelSpec::to_json() const {
     j.set("tie_embeddings", tie_embeddings);
     if (!position_table_name.empty()) j.set("position_table_name", position_table_name);
     if (logit_scale != 1.0) j.set("logit_scale", logit_scale);
+    if (embedding_scale != 1.0) j.set("embedding_scale", embedding_scale);
     j.set("embedding_name", embedding_name);
     j.set("final_norm_name", final_norm_name);
     j.set("head_name", head_name);
@@ -139,7 +140,7 @@ ModelSpec ModelSpec::from_json(const Json &j) {
         l.block = str_or(o, "block", "prenorm");
         l.mixer = PartSpec::from_json(o.get("mixer"));
         l.feed_forward = part_or_none(o.get("feed_forward"));
-        l.mixer_norm = PartSpec::from_json(o.get("mixer_norm"));
+        l.mixer_norm = part_or_none(o.get("mixer_norm"));
         l.ffn_norm = part_or_none(o.get("ffn_norm"));
         l.post_mixer_norm = part_or_none(o.get("post_mixer_norm"));
         l.post_ffn_norm = part_or_none(o.get("post_ffn_norm"));
@@ -166,6 +167,7 @@ ModelSpec ModelSpec::from_json(const Json &j) {
     s.tie_embeddings = j.get("tie_embeddings").as_bool();
     s.position_table_name = str_or(j, "position_table_name", "");
     if (j.get("logit_scale").is_number()) s.logit_scale = j.get("logit_scale").as_double();
+    if (j.get("embedding_scale").is_number()) s.embedding_scale = j.get("embedding_scale").as_double();
     s.embedding_name = str_or(j, "embedding_name", s.embedding_name);
     s.final_norm_name = str_or(j, "final_norm_name", s.final_norm_name);
     s.head_name = str_or(j, "head_name", s.head_name);

@@ -50,7 +50,8 @@ struct PartSpec {
 // fields are the sub-prefixes of its parts below it.
 //
 // A part whose kind is empty is absent: a layer may have no feed-forward (then it
-// needs no ffn_norm either), and only some block arrangements have norms on the
+// needs no ffn_norm either), an arrangement whose sublayers read the residual stream
+// itself has no mixer_norm, and only some block arrangements have norms on the
 // sublayers' results (post_mixer_norm, post_ffn_norm).  block_params are the
 // arrangement's own constants and the names of tensors it owns (gates on the
 // residual branches, for instance); they are found below `prefix` too.
@@ -96,6 +97,9 @@ struct ModelSpec {
     // embedding rows ("" for none), and a factor on the logits
     std::string position_table_name;
     double logit_scale = 1.0;
+    // a factor on the embedding rows as they enter the residual stream (a tied head reads
+    // the table without it)
+    double embedding_scale = 1.0;
     std::string embedding_name = "model.embed_tokens.weight";
     std::string final_norm_name = "model.norm";
     std::string head_name = "lm_head.weight";

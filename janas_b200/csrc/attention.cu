@@ -67,6 +67,12 @@ template <typename T> __device__ __forceinline__ void load_some(const T *p, floa
         out[j] = j < count ? to_f(p[j]) : 0.0f;
 }
 
+// Partials that the kept first tokens of a windowed mixer take: their chunks.
+__host__ __device__ inline int kept_chunks(int window, int keep_first)
+{
+    return window > 0 && keep_first > 0 ? (keep_first + ATT_CHUNK - 1) / ATT_CHUNK : 0;
+}
+
 // Scratch per (row, head, chunk index): m, l, then hd weighted values (hd: the
 // values' head size).
 __host__ __device__ inline size_t part_at(size_t row, int nh, int h, int max_chunks, int ci,
@@ -84,7 +90,8 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
                     int bt_stride, float *__restrict__ part, int row0, int n_rows, int nh, int nkv,
                     int hd, int vd, int window, float scale,
                     const float *__restrict__ head_scale, int max_chunks, int v_ld, float softcap,
-                    const float *__restrict__ slopes)
+                    const float *__restrict__ slopes, int keep_first,
+                    const float *__restrict__ score_bias)
 {
     constexpr int KPW = 32 / LPK;
     pdl_trigger();
@@ -103,10 +110,22 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
 
     int pos = row_pos[row];
     int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
-    int c = lo / ATT_CHUNK + ci;
-    if (c > pos / ATT_CHUNK)
-        return;
-    int t0 = max(lo, c * ATT_CHUNK), t1 = min(pos, c * ATT_CHUNK + ATT_CHUNK - 1);
+    // With kept first tokens the first kept_chunks(keep_first) partials of a row are
+    // those tokens' chunks, as far as they lie before the window; the window's chunks
+    // follow.  A partial whose range is empty is written as such (m = -inf, l = 0).
+    int kc = kept_chunks(window, keep_first);
+    int c, t0, t1;
+    if (ci < kc) {
+        c = ci;
+        t0 = c * ATT_CHUNK;
+        t1 = min(min(keep_first, lo) - 1, c * ATT_CHUNK + ATT_CHUNK - 1);
+    } else {
+        c = lo / ATT_CHUNK + ci - kc;
+        if (c > pos / ATT_CHUNK)
+            return;
+        t0 = max(lo, c * ATT_CHUNK);
+        t1 = min(pos, c * ATT_CHUNK + ATT_CHUNK - 1);
+    }
 
     int cidx = lane % LPK, ks = lane / LPK;
     // a lane's 16 values of the keys (and q) and of the values; heads that are no
@@ -143,6 +162,12 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
     for (int g = 0; g < ATT_GT; g++)
         sl[g] = slopes != nullptr && g < gt ? slopes[h0 + g] : 0.0f;
     float inv_cap = softcap > 0.0f ? 1.0f / softcap : 0.0f;
+    // a number per head added to the score, whose sigmoid is then the key's weight:
+    // no maximum, no sum of weights
+    float sb[ATT_GT];
+#pragma unroll
+    for (int g = 0; g < ATT_GT; g++)
+        sb[g] = score_bias != nullptr && g < gt ? score_bias[h0 + g] : 0.0f;
 
     for (int base = t0; base <= t1; base += KPW) {
         int t = base + ks;
@@ -190,7 +215,15 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
             for (int j = 0; j < 16; j++)
                 kv[j] = 0.0f;
         }
-        if (valid) {
+        if (valid && score_bias != nullptr) {
+#pragma unroll
+            for (int g = 0; g < ATT_GT; g++) {
+                float p = 1.0f / (1.0f + expf(-(s[g] + sb[g])));
+#pragma unroll
+                for (int j = 0; j < 16; j++)
+                    o[g][j] = fmaf(p, kv[j], o[g][j]);
+            }
+        } else if (valid) {
 #pragma unroll
             for (int g = 0; g < ATT_GT; g++) {
                 float mn = fmaxf(m[g], s[g]);
@@ -215,6 +248,8 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
             float mn = fmaxf(m[g], mo);
             float a = mn == -INFINITY ? 0.0f : expf(m[g] - mn);
             float b = mn == -INFINITY ? 0.0f : expf(mo - mn);
+            if (score_bias != nullptr)
+                a = b = 1.0f;           // plain sums
             l[g] = l[g] * a + lo_ * b;
             m[g] = mn;
 #pragma unroll
@@ -637,7 +672,7 @@ __global__ void attn_merge_kernel(const float *__restrict__ part,
                                   const int32_t *__restrict__ row_pos, T *__restrict__ out,
                                   int row0, int nh, int hd, int window, int max_chunks,
                                   int chunks_per_part, const float *__restrict__ sink,
-                                  long long head_major_rows)
+                                  long long head_major_rows, int keep_first, int plain_sum)
 {
     pdl_trigger();
     pdl_wait();
@@ -646,9 +681,23 @@ __global__ void attn_merge_kernel(const float *__restrict__ part,
     int pos = row_pos[row];
     int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
     // a partial covers chunks_per_part chunks; max_chunks is the partials' stride
-    int n_chunks = (pos / ATT_CHUNK - lo / ATT_CHUNK + chunks_per_part) / chunks_per_part;
+    int n_chunks = (pos / ATT_CHUNK - lo / ATT_CHUNK + chunks_per_part) / chunks_per_part +
+                   kept_chunks(window, keep_first);
     const float *base = part + part_at((size_t)lrow, nh, h, max_chunks, 0, hd);
     size_t stride = part_at(0, nh, 0, max_chunks, 1, hd);
+    if (plain_sum) {
+        // weights that are not normalized over the keys: the partials' sums, in chunk order
+        float acc = 0.0f;
+        if (d < hd) {
+            for (int c0 = 0; c0 < n_chunks; c0++)
+                acc += base[(size_t)c0 * stride + 2 + d];
+            if (head_major_rows > 0)
+                out[((size_t)h * head_major_rows + row) * hd + d] = from_f<T>(acc);
+            else
+                out[((size_t)row * nh + h) * hd + d] = from_f<T>(acc);
+        }
+        return;
+    }
     float m = -INFINITY, l = 0.0f, o = 0.0f;
     // a row with few partials fetches four at a time, one with more sixteen, one
     // with many thirty-two: most rows need one trip to memory
@@ -681,7 +730,8 @@ static int attention_typed(const T *q, const T *k_cache, const T *v_cache, const
                            float *part, T *out, int row0, int n_rows, int nh, int nkv, int hd,
                            int vd, int window, float scale, const float *head_scale,
                            const float *sink, int max_chunks, int v_ld, float softcap,
-                           const float *slopes, long long head_major_rows, cudaStream_t st)
+                           const float *slopes, long long head_major_rows, int keep_first,
+                           const float *score_bias, cudaStream_t st)
 {
     int lpk = 1;
     while (lpk * 16 < max(hd, vd))
@@ -692,7 +742,7 @@ static int attention_typed(const T *q, const T *k_cache, const T *v_cache, const
 #define JB_ATT(L)                                                                            \
     launch(attn_partial_kernel<T, L>, grid, 128, 0, st, q, k_cache, v_cache, row_pos, row_seq, \
            block_table, bt_stride, part, row0, n_rows, nh, nkv, hd, vd, window, scale,        \
-           head_scale, max_chunks, v_ld, softcap, slopes)
+           head_scale, max_chunks, v_ld, softcap, slopes, keep_first, score_bias)
     switch (lpk) {
     case 1: JB_ATT(1); break;
     case 2: JB_ATT(2); break;
@@ -706,7 +756,8 @@ static int attention_typed(const T *q, const T *k_cache, const T *v_cache, const
     if (cudaGetLastError() != cudaSuccess)
         return JB_ELAUNCH;
     launch(attn_merge_kernel<T>, dim3(n_rows, nh), (vd + 31) / 32 * 32, 0, st, (const float *)part,
-           row_pos, out, row0, nh, vd, window, max_chunks, 1, sink, head_major_rows);
+           row_pos, out, row0, nh, vd, window, max_chunks, 1, sink, head_major_rows, keep_first,
+           score_bias != nullptr ? 1 : 0);
     return launch_status();
 }
 
@@ -769,8 +820,34 @@ extern "C" int jb_attention_ext(const void *q, const void *k_cache, const void *
                                 const float *sink, int max_chunks, int v_ld, float softcap,
                                 const float *slopes, long long head_major_rows, cudaStream_t st)
 {
+    return jb_attention_gen(q, k_cache, v_cache, dt, row_pos, row_seq, block_table, bt_stride, scratch, out,
+                            row0, n_rows, nh, nkv, hd, vd, window, scale, head_scale, sink, max_chunks, v_ld,
+                            softcap, slopes, head_major_rows, 0, nullptr, st);
+}
+
+// The same with two more things.  keep_first > 0 (with a window): the first keep_first
+// positions of a sequence stay visible to every later row, beside the window; max_chunks
+// then counts their chunks too (jb_attention_kept_chunks).  score_bias (float [nh], or
+// null): a key's weight is sigmoid(score + score_bias[head]) and the weights are not
+// normalized over the keys (no softmax; a sink has no meaning then).
+extern "C" int jb_attention_kept_chunks(int window, int keep_first)
+{
+    return kept_chunks(window, keep_first);
+}
+
+extern "C" int jb_attention_gen(const void *q, const void *k_cache, const void *v_cache, int dt,
+                                const int32_t *row_pos, const int32_t *row_seq,
+                                const int32_t *block_table, int bt_stride, float *scratch,
+                                void *out, int row0, int n_rows, int nh, int nkv, int hd, int vd,
+                                int window, float scale, const float *head_scale,
+                                const float *sink, int max_chunks, int v_ld, float softcap,
+                                const float *slopes, long long head_major_rows, int keep_first,
+                                const float *score_bias, cudaStream_t st)
+{
     if (n_rows <= 0)
         return JB_OK;
+    if (keep_first < 0 || (score_bias != nullptr && sink != nullptr))
+        return JB_EINVAL;
     if (v_ld == 0)
         v_ld = vd;
     if (hd > 512 || hd <= 0 || vd > 512 || vd <= 0 || nkv <= 0 || nh % nkv || max_chunks <= 0 ||
@@ -782,12 +859,12 @@ extern "C" int jb_attention_ext(const void *q, const void *k_cache, const void *
                                       (const float *)v_cache, row_pos, row_seq, block_table,
                                       bt_stride, scratch, (float *)out, row0, n_rows, nh, nkv, hd,
                                       vd, window, scale, head_scale, sink, max_chunks, v_ld, softcap,
-                                      slopes, head_major_rows, st);
+                                      slopes, head_major_rows, keep_first, score_bias, st);
     // few rows over rows that are key and value at once for all heads: the chunk is
     // brought into shared memory once for all heads
     size_t ld_bytes = latent_decode_smem(nh, hd, vd);
     if (dt == JB_BF16 && nkv == 1 && v_cache == k_cache && v_ld == hd && head_scale == nullptr &&
-        softcap == 0.0f && slopes == nullptr && ld_bytes > 0 &&
+        softcap == 0.0f && slopes == nullptr && ld_bytes > 0 && keep_first == 0 && score_bias == nullptr &&
         (uintptr_t)q % 16 == 0 && (uintptr_t)k_cache % 16 == 0) {
         static unsigned long long smem_allowed = 0, mma_allowed = 0;
         size_t mma_bytes = latent_decode_mma_smem(nh, hd, vd);
@@ -806,7 +883,7 @@ extern "C" int jb_attention_ext(const void *q, const void *k_cache, const void *
         if (cudaGetLastError() != cudaSuccess)
             return JB_ELAUNCH;
         launch(attn_merge_kernel<bf16>, dim3(n_rows, nh), (vd + 31) / 32 * 32, 0, st, (const float *)scratch,
-               row_pos, (bf16 *)out, row0, nh, vd, window, max_chunks, 1, sink, head_major_rows);
+               row_pos, (bf16 *)out, row0, nh, vd, window, max_chunks, 1, sink, head_major_rows, 0, 0);
         return launch_status();
     }
     if (dt == JB_BF16)
@@ -814,7 +891,7 @@ extern "C" int jb_attention_ext(const void *q, const void *k_cache, const void *
                                      (const bf16 *)v_cache, row_pos, row_seq, block_table,
                                      bt_stride, scratch, (bf16 *)out, row0, n_rows, nh, nkv, hd,
                                      vd, window, scale, head_scale, sink, max_chunks, v_ld, softcap,
-                                     slopes, head_major_rows, st);
+                                     slopes, head_major_rows, keep_first, score_bias, st);
     return JB_EINVAL;
 }
 
@@ -844,10 +921,10 @@ extern "C" int jb_attention_merge_sink(const float *scratch, const int32_t *row_
     int threads = (hd + 31) / 32 * 32;
     if (dt == JB_F32)
         launch(attn_merge_kernel<float>, grid, threads, 0, st, scratch, row_pos, (float *)out, row0,
-               nh, hd, window, max_parts, chunks_per_part, sink, 0ll);
+               nh, hd, window, max_parts, chunks_per_part, sink, 0ll, 0, 0);
     else if (dt == JB_BF16)
         launch(attn_merge_kernel<bf16>, grid, threads, 0, st, scratch, row_pos, (bf16 *)out, row0,
-               nh, hd, window, max_parts, chunks_per_part, sink, 0ll);
+               nh, hd, window, max_parts, chunks_per_part, sink, 0ll, 0, 0);
     else
         return JB_EINVAL;
     return launch_status();

@@ -96,6 +96,14 @@ int jb_attention_ext(const void *q, const void *k_cache, const void *v_cache, in
                      int nkv, int hd, int vd, int window, float scale, const float *head_scale,
                      const float *sink, int max_chunks, int v_ld, float softcap,
                      const float *slopes, long long head_major_rows, cudaStream_t st);
+int jb_attention_kept_chunks(int window, int keep_first);
+int jb_attention_gen(const void *q, const void *k_cache, const void *v_cache, int dt,
+                     const int32_t *row_pos, const int32_t *row_seq, const int32_t *block_table,
+                     int bt_stride, float *scratch, void *out, int row0, int n_rows, int nh,
+                     int nkv, int hd, int vd, int window, float scale, const float *head_scale,
+                     const float *sink, int max_chunks, int v_ld, float softcap,
+                     const float *slopes, long long head_major_rows, int keep_first,
+                     const float *score_bias, cudaStream_t st);
 int jb_layernorm(float *x, const float *a, int Sa, long long a_stride, const float *b, int Sb,
                  long long b_stride, float mult, const int32_t *row_idx, const float *w,
                  const float *bias, void *out, int out_dt, int n_out, int dm, float eps,
@@ -123,6 +131,33 @@ int jb_heads_gate(const float *A, int S, int nh, int Dv, const float *g, int Sg,
 int jb_transpose_heads(const void *in, void *out, int dt, int H, int D, int C, cudaStream_t st);
 int jb_activation(const float *z, int S, long long stride, int ld, int kind, void *out, int out_dt,
                   int n, int ff, cudaStream_t st);
+int jb_qkv_prepare_append(const float *qkv, int S, long long split_stride, int ld, const float *bias,
+                          const float *q_w, const float *k_w, float eps, const float *cs,
+                          const float *sn, int rot_half, const int32_t *row_pos,
+                          const int32_t *row_seq, const int32_t *block_table, int bt_stride,
+                          void *q_out, void *k_cache, void *v_cache, int cache_dt, int n, int nh,
+                          int nkv, int hd, int vd, cudaStream_t st);
+int jb_norm_residual(float *x, const float *a, int Sa, long long a_stride, const float *a_bias,
+                     const void *skip, int skip_dt, const float *coef, int coef_ld, const float *w,
+                     const float *bias, int n, int dm, float eps, int rms, int few_rows,
+                     cudaStream_t st);
+int jb_short_conv(const float *x, const float *w, float *state, long long slot_stride, const int32_t *row_pos,
+                  const int32_t *row_seq, const int32_t *seq_slot, void *out, int out_dt, int n,
+                  int dm, int taps, int what, cudaStream_t st);
+int jb_mingru_piece(void);
+long long jb_mingru_scratch(int n, int n_seqs, int W, int every_row_starts);
+int jb_mingru(const float *P, int S, long long stride, int ld, int col0, const float *bias,
+              float *state, const int32_t *row_seq, const int32_t *seq_slot, float *scratch,
+              void *out, int out_dt, int n, int n_seqs, int W, int every_row_starts,
+              cudaStream_t st);
+int jb_moe_route(const float *P, int S, long long stride, int ld, int col0, const float *correction,
+                 float *weights, float *skip_coef, int n, int E, int groups, int keep, int top,
+                 int first_identity, float scale, cudaStream_t st);
+int jb_activation_weighted(const float *z, int S, long long stride, int ld, const float *weights,
+                           int w_ld, int n_experts, int ff, int kind, void *out, int out_dt, int n,
+                           int width, cudaStream_t st);
+int jb_add_row_scaled(float *y, const void *skip, int skip_dt, const float *coef, int coef_ld, int n, int m,
+                      cudaStream_t st);
 int jb_attn_tc_decode_runs(int nh, int nkv, int hd);
 int jb_attn_tc_ok(int nh, int nkv, int hd);
 int jb_attn_tc_block_positions(int nh, int nkv);

@@ -169,6 +169,80 @@ void add_scaled_(Device &d, float *x, long long n, long long dm, const Stack &a,
                        as_int(dm, "width"), 0.0f, d.stream), "add_scaled");
 }
 
+void norm_residual_(Device &d, float *x, const Stack &y, const LnParams &p, bool rms, bool few_rows) {
+    if (!y) fail(JB_LLM_EINVAL, "norm_residual: no result to norm");
+    check(jb_norm_residual(x, y.data(), y.S, y.stride(), y.bias, y.skip, y.skip_dt, y.skip_coef,
+                           (int)y.skip_coef_ld, p.w, p.b, as_int(y.n, "rows"), as_int(y.m, "width"), p.eps,
+                           rms ? 1 : 0, few_rows ? 1 : 0, d.stream), "norm_residual");
+}
+
+Buf short_conv(Device &d, const float *x, long long n, long long dm, const float *w, int taps, float *state,
+               long long slot_stride, const int32_t *row_pos, const int32_t *row_seq, const int32_t *seq_slot, DType out_dt,
+               bool write_h, bool write_state) {
+    need_float(out_dt, "short_conv output");
+    Buf out;
+    if (write_h) out = d.pool.get((size_t)n * (size_t)dm * dtype_size(out_dt));
+    int what = (write_h ? 1 : 0) | (write_state ? 2 : 0);
+    if (!what) return out;
+    check(jb_short_conv(x, w, state, slot_stride, row_pos, row_seq, seq_slot, out.ptr, out_dt, as_int(n, "rows"),
+                        as_int(dm, "width"), taps, what, d.stream), "short_conv");
+    return out;
+}
+
+Buf mingru(Device &d, const Stack &P, long long col0, long long W, const float *bias, float *state,
+           const int32_t *row_seq, const int32_t *seq_slot, int n_seqs, bool every_row_starts, DType out_dt) {
+    need_float(out_dt, "mingru output");
+    if (P.m < col0 + 3 * W) fail(JB_LLM_EINVAL, "mingru: the product is narrower than z, x and g");
+    int n = as_int(P.n, "rows"), w = as_int(W, "width");
+    long long need = jb_mingru_scratch(n, n_seqs, w, every_row_starts ? 1 : 0);
+    Buf scratch;
+    if (need > 0) scratch = d.pool.get((size_t)need * 4);
+    Buf out = d.pool.get((size_t)P.n * (size_t)W * dtype_size(out_dt));
+    check(jb_mingru(P.data(), P.S, P.stride(), as_int(P.m, "width"), (int)col0, bias, state, row_seq, seq_slot,
+                    scratch.as<float>(), out.ptr, out_dt, n, n_seqs, w, every_row_starts ? 1 : 0, d.stream),
+          "mingru", need > 0 ? 3 : 1);
+    return out;
+}
+
+Buf moe_route(Device &d, const Stack &P, long long col0, const RouteParams &r, Buf *skip_coef) {
+    if (P.m < col0 + r.experts) fail(JB_LLM_EINVAL, "moe_route: the product is narrower than the router's rows");
+    Buf weights = d.pool.get(std::max<size_t>((size_t)P.n * (size_t)r.experts * 4, 16));
+    if (skip_coef) *skip_coef = d.pool.get(std::max<size_t>((size_t)P.n * 4, 16));
+    check(jb_moe_route(P.data(), P.S, P.stride(), as_int(P.m, "width"), (int)col0, r.correction,
+                       weights.as<float>(), skip_coef ? skip_coef->as<float>() : nullptr, as_int(P.n, "rows"),
+                       r.experts, r.groups, r.keep, r.top, r.first_identity, r.scale, d.stream), "moe_route");
+    return weights;
+}
+
+Buf activation_weighted(Device &d, const Stack &z, long long width, const float *weights, int w_ld, int n_experts,
+                        long long ff, int kind, DType out_dt) {
+    need_float(out_dt, "activation output");
+    if (width <= 0 || width > z.m) fail(JB_LLM_EINVAL, "activation_weighted: the product is narrower than the experts");
+    Buf out = d.pool.get((size_t)z.n * (size_t)width * dtype_size(out_dt));
+    check(jb_activation_weighted(z.data(), z.S, z.stride(), as_int(z.m, "width"), weights, w_ld, n_experts,
+                                 as_int(ff, "width"), kind, out.ptr, out_dt, as_int(z.n, "rows"),
+                                 as_int(width, "width"), d.stream), "activation_weighted");
+    return out;
+}
+
+Buf qkv_prepare_append(Device &d, const Stack &qkv, const float *bias, const float *q_w, const float *k_w,
+                       float eps, const float *cos, const float *sin, int rot_half, const int32_t *row_pos,
+                       const int32_t *row_seq, const AttnCache &c, const AttnGeometry &g, DType out_dt) {
+    bool append = c.writes;
+    long long width = (long long)g.nh * g.hd + (append ? (long long)g.nkv * (g.hd + g.value_dim()) : 0);
+    if (qkv.m < width) fail(JB_LLM_EINVAL, "qkv_prepare_append: the product is narrower than q, k and v");
+    if (append && (!c.k || !c.v)) fail(JB_LLM_EINVAL, "qkv_prepare_append: no cache to append to");
+    if (append && c.dt != out_dt) fail(JB_LLM_EINVAL, "qkv_prepare_append: the cache is of another type");
+    Buf q = d.pool.get((size_t)qkv.n * (size_t)g.nh * (size_t)g.hd * dtype_size(out_dt));
+    check(jb_qkv_prepare_append(qkv.data(), qkv.S, qkv.stride(), as_int(qkv.m, "width"), bias, q_w, k_w, eps, cos,
+                                sin, rot_half, row_pos, row_seq, c.block_table, c.bt_stride, q.ptr,
+                                append ? c.k : nullptr, append ? c.v : nullptr, out_dt, as_int(qkv.n, "rows"),
+                                g.nh, g.nkv, g.hd, g.value_dim(), d.stream), "qkv_prepare_append");
+    return q;
+}
+
+int attention_kept_chunks(int window, int keep_first) { return jb_attention_kept_chunks(window, keep_first); }
+
 int activation_kind(const std::string &name) {
     if (name == "relu2") return JB_ACT_RELU2;
     if (name == "relu") return JB_ACT_RELU;
@@ -289,9 +363,18 @@ void add_bias_(Device &d, float *y, long long n, long long m, const float *bias)
 }
 
 void resolve_bias(Device &d, Stack &y) {
-    if (!y.bias || !y) return;
-    add_bias_(d, y.data(), y.n, y.m, y.bias);
-    y.bias = nullptr;
+    if (!y) return;
+    if (y.bias) {
+        add_bias_(d, y.data(), y.n, y.m, y.bias);
+        y.bias = nullptr;
+    }
+    if (y.skip) {
+        check(jb_add_row_scaled(y.data(), y.skip, y.skip_dt, y.skip_coef, (int)y.skip_coef_ld, as_int(y.n, "rows"),
+                                as_int(y.m, "width"), d.stream), "add_row_scaled");
+        y.skip = nullptr;
+        y.skip_coef = nullptr;
+        y.skip_hold.reset();
+    }
 }
 
 void add_(Device &d, float *x, long long n, long long dm, const Stack &delta) {
@@ -463,7 +546,7 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
     int vd = g.value_dim();
     Buf out = d.pool.get((size_t)n * (size_t)g.nh * (size_t)vd * dtype_size(c.dt));
     bool tc = !force_simt && vd == g.hd && c.dt == BF16 && (decode || blocks != nullptr) &&
-              !c.v_ld && !head_major &&
+              !c.v_ld && !head_major && !g.keep_first && !g.score_bias &&
               attention_tc_ok(g.nh, g.nkv, g.hd) && (decode || !g.head_scale || g.head_scale_positive);
     if (tc && !decode) {
         check(jb_attn_tc_prefill_ext(q, c.k, c.v, c.n_pages, blocks, n_blocks, c.block_table, c.bt_stride,
@@ -493,10 +576,10 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
             check(jb_attention_merge_sink(scratch.as<float>(), row_pos, out.ptr, c.dt, (int)row0, cnt, g.nh,
                                           g.hd, g.window, parts, per_cta, g.sink, d.stream), "attention merge");
         } else {
-            check(jb_attention_ext(q, c.k, c.v, c.dt, row_pos, row_seq, c.block_table, c.bt_stride,
+            check(jb_attention_gen(q, c.k, c.v, c.dt, row_pos, row_seq, c.block_table, c.bt_stride,
                                    scratch.as<float>(), out.ptr, (int)row0, cnt, g.nh, g.nkv, g.hd, vd,
                                    g.window, g.scale, g.head_scale, g.sink, max_chunks, c.v_ld, g.softcap,
-                                   g.slopes, head_major ? n : 0, d.stream),
+                                   g.slopes, head_major ? n : 0, g.keep_first, g.score_bias, d.stream),
                   "attention", 2);
         }
     }

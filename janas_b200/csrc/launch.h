@@ -28,6 +28,15 @@ struct Stack {
     // product's bias), or null.  The kernels that end a sublayer take it as it is;
     // for every other consumer resolve_bias() adds it into the first partial sum.
     const float *bias = nullptr;
+    // Also still to be added: skip_coef[r * skip_coef_ld] * skip[r, :] for every row r (a
+    // part's own input handed on with a weight per row: the identity experts of a routed
+    // feed-forward).  skip: [n, m] of type skip_dt; null: nothing.  The kernel that ends a
+    // sublayer with a norm on its result takes it; no other consumer does.
+    const void *skip = nullptr;
+    DType skip_dt = F32;
+    const float *skip_coef = nullptr;
+    long long skip_coef_ld = 1;
+    Buf skip_hold;                      // keeps skip_coef's memory
     float *data() const { return (float *)buf.ptr; }
     long long stride() const { return n * m; }
     explicit operator bool() const { return S > 0; }
@@ -86,6 +95,39 @@ void add_scaled_(Device &d, float *x, long long n, long long dm, const Stack &a,
 int activation_kind(const std::string &name);       // -1: unknown
 Buf activation(Device &d, const Stack &z, long long ff, int kind, DType out_dt);
 
+// x += norm(sum y + y.bias + y's skip term) w (+ b): a norm on a sublayer's result alone,
+// added to the residual stream in place.  rms: no mean is taken off.  few_rows: the
+// bfloat16 path's kernel for a decode step's rows.
+void norm_residual_(Device &d, float *x, const Stack &y, const LnParams &p, bool rms, bool few_rows);
+
+// h = x + a causal convolution over time on every channel (w: float32 [dm, taps]), as
+// [n, dm] in out_dt; state: float32 [taps - 1, dm] per slot, slot_stride floats apart (null
+// with taps == 1).  write_h /
+// write_state: what this launch does (see csrc/recurrent.cu for when both may be one).
+Buf short_conv(Device &d, const float *x, long long n, long long dm, const float *w, int taps, float *state,
+               long long slot_stride, const int32_t *row_pos, const int32_t *row_seq, const int32_t *seq_slot, DType out_dt,
+               bool write_h, bool write_state);
+
+// The minGRU's recurrence over the rows, from the sums P of [z | x | g] (columns col0 ..,
+// W each; bias float32 [3 W] or null): S * silu(g) as [n, W] in out_dt; state: float32
+// [slots, W], read and left updated.  every_row_starts: a decode step.
+Buf mingru(Device &d, const Stack &P, long long col0, long long W, const float *bias, float *state,
+           const int32_t *row_seq, const int32_t *seq_slot, int n_seqs, bool every_row_starts, DType out_dt);
+
+// The router of a routed feed-forward (csrc/moe.cu): weights [n, E] float32 (0 for experts
+// not chosen) and, with skip_coef, the summed weight of the chosen experts from
+// first_identity on.
+struct RouteParams {
+    int experts = 0, groups = 1, keep = 1, top = 1, first_identity = 0;
+    float scale = 1.0f;
+    const float *correction = nullptr;
+};
+Buf moe_route(Device &d, const Stack &P, long long col0, const RouteParams &r, Buf *skip_coef);
+// act(sum z) * weights[row, column / ff] over the first n_experts * ff columns of z, act
+// alone over the rest up to width: [n, width] in out_dt.  weights: float32 [n, w_ld].
+Buf activation_weighted(Device &d, const Stack &z, long long width, const float *weights, int w_ld, int n_experts,
+                        long long ff, int kind, DType out_dt);
+
 // RMSNorm of the rows of x (float32 [n, dm]).  With delta, x is first updated in
 // place, x += delta[0] + ... + delta[S-1].  With rows (n_out int32 indices on the
 // device) only those rows are normalized and returned, in that order; delta and
@@ -135,6 +177,8 @@ struct AttnGeometry {
     const float *head_scale = nullptr;       // float32 [nh] on the device: a factor per head on the scores
     const float *sink = nullptr;             // float32 [nh]: exp(sink) joins each softmax's denominator
     bool head_scale_positive = true;         // every factor is > 0 (the prefill tensor-core kernel needs it)
+    int keep_first = 0;                      // with a window: the first positions stay visible to all later rows
+    const float *score_bias = nullptr;       // float32 [nh]: a key's weight is sigmoid(score + bias), not normalized
     int value_dim() const { return vd > 0 ? vd : hd; }
 };
 
@@ -191,6 +235,15 @@ void latent_q_join(Device &d, const HeadStack &A, long long R, void *q_lat, DTyp
 Buf heads_gate(Device &d, const HeadStack &A, const Stack &g, long long g_col0, DType out_dt);
 // w viewed as [H, rows / H, cols] -> [H, cols, rows / H], a new tensor of the same type
 DevTensor transpose_heads(Device &d, const DevTensor &w, int H);
+
+// q, k, v out of the fused product's sums (bias: float32 over its columns or null): per-head
+// RMS norm of q and k (weights float32 [hd], or null), rotation of the first 2 rot_half
+// values of a head, K and V (of their own head size) into the cache.  Returns q [n, heads, hd].
+Buf qkv_prepare_append(Device &d, const Stack &qkv, const float *bias, const float *q_w, const float *k_w,
+                       float eps, const float *cos, const float *sin, int rot_half, const int32_t *row_pos,
+                       const int32_t *row_seq, const AttnCache &c, const AttnGeometry &g, DType out_dt);
+// chunks that the kept first tokens of a windowed mixer add to a row's range
+int attention_kept_chunks(int window, int keep_first);
 
 // The blocks a prefill step is cut into for the tensor-core kernel: int32
 // [blocks, 4] = first row, positions, the first row's position, sequence;

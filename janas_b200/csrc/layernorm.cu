@@ -142,9 +142,147 @@ layernorm_cluster_kernel(float *__restrict__ x, const float *__restrict__ a, int
         o[i] = from_f<TO>(fmaf((row[i - c0] - mean) * inv, w[i], bias != nullptr ? bias[i] : 0.0f));
 }
 
+
+// A norm on a sublayer's result alone, added to the residual stream:
+//
+//   y   = sum_s a[s] + a_bias + coef[r] * skip[r]        (the last two optional)
+//   x  <- x + (y - mean y) / sqrt(var y + eps) * w + bias
+//
+// skip is the sublayer's own input in its storage type TS (what an identity expert of a
+// routed feed-forward hands on), coef one number per row.  One block per row, the row of
+// y in shared memory, two passes as above.  rms = 1: no mean is taken off (RMS norm).
+template <typename TS>
+__global__ void __launch_bounds__(256)
+norm_residual_kernel(float *__restrict__ x, const float *__restrict__ a, int Sa, size_t a_stride,
+                     const float *__restrict__ a_bias, const TS *__restrict__ skip,
+                     const float *__restrict__ coef, int coef_ld, const float *__restrict__ w,
+                     const float *__restrict__ bias, int dm, float eps, int rms)
+{
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    pdl_trigger();
+    int r = blockIdx.x;
+    pdl_wait();
+    float sum = 0.0f;
+    float c = skip != nullptr ? coef[(size_t)r * coef_ld] : 0.0f;
+    for (int i = threadIdx.x; i < dm; i += blockDim.x) {
+        float v = add_partials(a_bias != nullptr ? a_bias[i] : 0.0f, a + (size_t)r * dm + i, Sa, a_stride);
+        if (skip != nullptr)
+            v = fmaf(c, to_f(skip[(size_t)r * dm + i]), v);
+        row[i] = v;
+        sum += v;
+    }
+    float mean = rms ? 0.0f : block_sum(sum, red) / (float)dm;
+    float sq = 0.0f;
+    for (int i = threadIdx.x; i < dm; i += blockDim.x) {
+        float d = row[i] - mean;
+        sq = fmaf(d, d, sq);
+    }
+    float var = block_sum(sq, red) / (float)dm;
+    float inv = 1.0f / sqrtf(var + eps);
+    float *xr = x + (size_t)r * dm;
+    for (int i = threadIdx.x; i < dm; i += blockDim.x)
+        xr[i] += fmaf((row[i] - mean) * inv, w[i], bias != nullptr ? bias[i] : 0.0f);
+}
+
+// The same for few rows of the bfloat16 path: a cluster of C CTAs per row (see
+// layernorm_cluster_kernel).
+template <typename TS, int C>
+__global__ void __launch_bounds__(256)
+norm_residual_cluster_kernel(float *__restrict__ x, const float *__restrict__ a, int Sa, size_t a_stride,
+                             const float *__restrict__ a_bias, const TS *__restrict__ skip,
+                             const float *__restrict__ coef, int coef_ld, const float *__restrict__ w,
+                             const float *__restrict__ bias, int dm, int cols, float eps, int rms)
+{
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    __shared__ float part_sum[C], part_sq[C];
+    pdl_trigger();
+    uint32_t rank = cluster_rank();
+    int r = blockIdx.x / C;
+    int c0 = (int)rank * cols, c1 = min(dm, c0 + cols);
+    pdl_wait();
+    float sum = 0.0f;
+    float c = skip != nullptr ? coef[(size_t)r * coef_ld] : 0.0f;
+    for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) {
+        float v = add_partials(a_bias != nullptr ? a_bias[i] : 0.0f, a + (size_t)r * dm + i, Sa, a_stride);
+        if (skip != nullptr)
+            v = fmaf(c, to_f(skip[(size_t)r * dm + i]), v);
+        row[i - c0] = v;
+        sum += v;
+    }
+    sum = block_sum(sum, red);
+    if (threadIdx.x < C)
+        cluster_write(&part_sum[rank], threadIdx.x, sum);
+    cluster_arrive();
+    cluster_wait();
+    float tot = 0.0f;
+#pragma unroll
+    for (int k = 0; k < C; k++)
+        tot += part_sum[k];
+    float mean = rms ? 0.0f : tot / (float)dm;
+    float sq = 0.0f;
+    for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) {
+        float d = row[i - c0] - mean;
+        sq = fmaf(d, d, sq);
+    }
+    sq = block_sum(sq, red);
+    if (threadIdx.x < C)
+        cluster_write(&part_sq[rank], threadIdx.x, sq);
+    cluster_arrive();
+    cluster_wait();
+    tot = 0.0f;
+#pragma unroll
+    for (int k = 0; k < C; k++)
+        tot += part_sq[k];
+    float inv = 1.0f / sqrtf(tot / (float)dm + eps);
+    float *xr = x + (size_t)r * dm;
+    for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x)
+        xr[i] += fmaf((row[i - c0] - mean) * inv, w[i], bias != nullptr ? bias[i] : 0.0f);
+}
+
 }  // namespace jb
 
 using namespace jb;
+
+// x: float32 [n, dm], updated in place.  a: S stacked [n, dm] partial sums of the
+// sublayer's result; a_bias: float32 [dm] or null; skip: [n, dm] of type skip_dt with
+// coef (float32, one per row, coef_ld apart) or null; w, bias: float32 [dm] (bias may be
+// null); rms: 1 for an RMS norm.  few_rows: a cluster of CTAs per row (the bfloat16 path's
+// decode steps; the 32-bit path never sets it, so a row's bits do not depend on the batch).
+extern "C" int jb_norm_residual(float *x, const float *a, int Sa, long long a_stride, const float *a_bias,
+                                const void *skip, int skip_dt, const float *coef, int coef_ld,
+                                const float *w, const float *bias, int n, int dm, float eps, int rms,
+                                int few_rows, cudaStream_t st)
+{
+    if (n <= 0)
+        return JB_OK;
+    if (dm <= 0 || dm > 49152 / 4 || a == nullptr || Sa <= 0 || w == nullptr ||
+        (skip != nullptr && (coef == nullptr || coef_ld <= 0)))
+        return JB_EINVAL;
+    constexpr int CL = 8;
+    bool cluster = few_rows && n <= 32 && dm >= 64 * CL;
+    int cols = (dm + CL - 1) / CL;
+    unsigned threads = (unsigned)min(256, ((cluster ? cols : dm) + 31) / 32 * 32);
+#define JB_NR(TS)                                                                                       \
+    do {                                                                                                \
+        if (cluster)                                                                                    \
+            launch_cluster(norm_residual_cluster_kernel<TS, CL>, dim3((unsigned)n * CL), threads,       \
+                           (size_t)cols * 4, st, CL, x, a, Sa, (size_t)a_stride, a_bias, (const TS *)skip, \
+                           coef, coef_ld, w, bias, dm, cols, eps, rms);                                 \
+        else                                                                                            \
+            launch(norm_residual_kernel<TS>, (unsigned)n, threads, (size_t)dm * 4, st, x, a, Sa,        \
+                   (size_t)a_stride, a_bias, (const TS *)skip, coef, coef_ld, w, bias, dm, eps, rms);   \
+    } while (0)
+    if (skip == nullptr || skip_dt == JB_F32)
+        JB_NR(float);
+    else if (skip_dt == JB_BF16)
+        JB_NR(bf16);
+    else
+        return JB_EINVAL;
+#undef JB_NR
+    return launch_status();
+}
 
 // x: float32 [n, dm], updated in place when a is given (b only together with a).
 // row_idx (n_out int32, or null): the rows to normalize; with row_idx no add is

@@ -1,0 +1,267 @@
+// Recurrences along a sequence whose state is of fixed size: a short causal
+// convolution over time on every channel of the residual stream, and the minGRU's
+// gated running value.  The state lives per slot in float32 and is carried from
+// step to step; everything here is computed in float32.
+//
+// Rows are the sequences' tokens one sequence after the other; row r belongs to
+// sequence row_seq[r] of the step (slot seq_slot[row_seq[r]]) and stands at position
+// row_pos[r].  The rows of one sequence are consecutive, so "the row k before r is of
+// the same sequence" is row_seq[r - k] == row_seq[r].
+#include "common.cuh"
+#include "kernels.h"
+
+namespace jb {
+
+// ------------------------------------------------------------ short convolution
+//
+//   h_t = x_t + sum_{j < taps} w[:, j] * x_{t - taps + 1 + j}        (zeros before position 0)
+//
+// x: float32 [n, dm]; w: float32 [dm, taps].  state: float32 [taps - 1, dm] per slot,
+// slot_stride floats from one slot's to the next's: the
+// input at position p of a slot's sequence lies in row p % (taps - 1) until a later
+// position takes the row.  Inputs of earlier steps are read from there, inputs of this
+// step from x.  what & 1: h is written; what & 2: the rows that are among the last
+// taps - 1 of their sequence in this step write their input into the state.  Both at
+// once only where no row reads a state row that another row of the step writes: every
+// sequence starts at position 0 (nothing is read) or brings one row (a thread reads
+// before it writes its own).
+template <typename TO, int V>
+__global__ void __launch_bounds__(256)
+short_conv_kernel(const float *__restrict__ x, const float *__restrict__ w, float *__restrict__ state,
+                  size_t slot_stride, const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
+                  const int32_t *__restrict__ seq_slot, TO *__restrict__ out, int n, int dm, int taps,
+                  int what)
+{
+    pdl_trigger();
+    int per_row = dm / V;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n * per_row)
+        return;
+    int r = (int)(idx / per_row), c = (int)(idx - (size_t)r * per_row) * V;
+    int pos = row_pos[r], seq = row_seq[r];
+    int slot = seq_slot[seq];
+    int keep = taps - 1;
+    pdl_wait();
+    float cur[V];
+#pragma unroll
+    for (int v = 0; v < V; v++)
+        cur[v] = x[(size_t)r * dm + c + v];
+    float *st = state != nullptr ? state + (size_t)slot * slot_stride : nullptr;
+    if (what & 1) {
+        float acc[V];
+#pragma unroll
+        for (int v = 0; v < V; v++)
+            acc[v] = fmaf(w[(size_t)(c + v) * taps + taps - 1], cur[v], cur[v]);
+        for (int k = 1; k <= keep; k++) {
+            int p = pos - k;
+            if (p < 0)
+                break;
+            const float *src = r - k >= 0 && row_seq[r - k] == seq ? x + (size_t)(r - k) * dm
+                                                                  : st + (size_t)(p % keep) * dm;
+#pragma unroll
+            for (int v = 0; v < V; v++)
+                acc[v] = fmaf(w[(size_t)(c + v) * taps + taps - 1 - k], src[c + v], acc[v]);
+        }
+#pragma unroll
+        for (int v = 0; v < V; v++)
+            out[(size_t)r * dm + c + v] = from_f<TO>(acc[v]);
+    }
+    if ((what & 2) && keep > 0 && (r + keep >= n || row_seq[r + keep] != seq)) {
+#pragma unroll
+        for (int v = 0; v < V; v++)
+            st[(size_t)(pos % keep) * dm + c + v] = cur[v];
+    }
+}
+
+// ---------------------------------------------------------------------- minGRU
+//
+//   z = sigmoid(P_z + b_z);  u = P_x + b_x;  c = u + 1/2 (u >= 0), sigmoid(u) (u < 0)
+//   S_t = (1 - z_t) S_{t-1} + z_t c_t;   out_t = S_t * silu(P_g)
+//
+// P: the sums [S, n, ld] of one product over the mixer's input whose columns are
+// [z | x | g] from col0 on, W each; bias: float32 [3 W] over those columns or null.
+// state: float32 [slots, W], a sequence's S after its last computed token.
+struct GruIn {
+    const float *P;
+    int S;
+    size_t stride;
+    int ld, col0;
+    const float *bias;
+    int W;
+};
+
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+// a_t = 1 - z_t, b_t = z_t c_t of (row, channel)
+__device__ __forceinline__ void gru_coef(const GruIn &in, int r, int ch, float &a, float &b)
+{
+    const float *p = in.P + (size_t)r * in.ld + in.col0 + ch;
+    float z = sigmoidf_(add_partials(in.bias != nullptr ? in.bias[ch] : 0.0f, p, in.S, in.stride));
+    float u = add_partials(in.bias != nullptr ? in.bias[in.W + ch] : 0.0f, p + in.W, in.S, in.stride);
+    float c = u >= 0.0f ? u + 0.5f : sigmoidf_(u);
+    a = 1.0f - z;
+    b = z * c;
+}
+
+// Rows are cut into pieces of `piece` consecutive rows of the step; a thread owns one
+// channel of one piece.  Over a piece the recurrence is S -> A S + B; the first row of a
+// sequence within the step starts from the slot's state instead (A = 0).  This kernel
+// leaves A and B of every piece in AB [pieces, 2, W] and a copy of the state each
+// sequence starts from in init [sequences, W].
+__global__ void __launch_bounds__(128)
+mingru_pieces_kernel(GruIn in, const float *__restrict__ state, const int32_t *__restrict__ row_seq,
+                     const int32_t *__restrict__ seq_slot, float *__restrict__ AB, float *__restrict__ init,
+                     int n, int piece)
+{
+    pdl_trigger();
+    int ch = blockIdx.x * blockDim.x + threadIdx.x, pc = blockIdx.y;
+    if (ch >= in.W)
+        return;
+    pdl_wait();
+    int r0 = pc * piece, r1 = min(n, r0 + piece);
+    float A = 1.0f, B = 0.0f;
+    for (int r = r0; r < r1; r++) {
+        float a, b;
+        gru_coef(in, r, ch, a, b);
+        int seq = row_seq[r];
+        if (r == 0 || row_seq[r - 1] != seq) {
+            float s0 = state[(size_t)seq_slot[seq] * in.W + ch];
+            init[(size_t)seq * in.W + ch] = s0;
+            A = 0.0f;
+            B = fmaf(a, s0, b);
+        } else {
+            A *= a;
+            B = fmaf(a, B, b);
+        }
+    }
+    AB[((size_t)pc * 2) * in.W + ch] = A;
+    AB[((size_t)pc * 2 + 1) * in.W + ch] = B;
+}
+
+// The value each piece starts from: carry [pieces, W], piece after piece.
+__global__ void __launch_bounds__(128)
+mingru_carry_kernel(const float *__restrict__ AB, float *__restrict__ carry, int W, int pieces)
+{
+    pdl_trigger();
+    int ch = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ch >= W)
+        return;
+    pdl_wait();
+    float s = 0.0f;
+    for (int pc = 0; pc < pieces; pc++) {
+        carry[(size_t)pc * W + ch] = s;
+        s = fmaf(AB[((size_t)pc * 2) * W + ch], s, AB[((size_t)pc * 2 + 1) * W + ch]);
+    }
+}
+
+// The recurrence itself over each piece, from the piece's carry (null: nothing is
+// carried into a piece: one piece in all, or every row starts a sequence), with the
+// output and the new state.  init null: a sequence's start is read from the state
+// itself (only where the thread that reads it is the one that writes it: one piece, or
+// one row per sequence).
+template <typename TO>
+__global__ void __launch_bounds__(128)
+mingru_scan_kernel(GruIn in, float *__restrict__ state, const int32_t *__restrict__ row_seq,
+                   const int32_t *__restrict__ seq_slot, const float *__restrict__ carry,
+                   const float *__restrict__ init, TO *__restrict__ out, int n, int piece)
+{
+    pdl_trigger();
+    int ch = blockIdx.x * blockDim.x + threadIdx.x, pc = blockIdx.y;
+    if (ch >= in.W)
+        return;
+    pdl_wait();
+    int r0 = pc * piece, r1 = min(n, r0 + piece);
+    float s = carry != nullptr ? carry[(size_t)pc * in.W + ch] : 0.0f;
+    for (int r = r0; r < r1; r++) {
+        float a, b;
+        gru_coef(in, r, ch, a, b);
+        int seq = row_seq[r];
+        if (r == 0 || row_seq[r - 1] != seq)
+            s = init != nullptr ? init[(size_t)seq * in.W + ch] : state[(size_t)seq_slot[seq] * in.W + ch];
+        s = fmaf(a, s, b);
+        float g = add_partials(in.bias != nullptr ? in.bias[2 * in.W + ch] : 0.0f,
+                               in.P + (size_t)r * in.ld + in.col0 + 2 * in.W + ch, in.S, in.stride);
+        out[(size_t)r * in.W + ch] = from_f<TO>(s * (g * sigmoidf_(g)));
+        if (r + 1 == n || row_seq[r + 1] != seq)
+            state[(size_t)seq_slot[seq] * in.W + ch] = s;
+    }
+}
+
+}  // namespace jb
+
+using namespace jb;
+
+// what: 1 = write h, 2 = write the state, 3 = both (see short_conv_kernel for when).
+// state may be null with taps == 1.
+extern "C" int jb_short_conv(const float *x, const float *w, float *state, long long slot_stride,
+                             const int32_t *row_pos,
+                             const int32_t *row_seq, const int32_t *seq_slot, void *out, int out_dt, int n,
+                             int dm, int taps, int what, cudaStream_t st)
+{
+    if (n <= 0)
+        return JB_OK;
+    if (dm <= 0 || taps < 1 || (taps > 1 && (state == nullptr || slot_stride < (long long)(taps - 1) * dm)) || !(what & 3) ||
+        ((what & 1) && out == nullptr))
+        return JB_EINVAL;
+    bool vec = dm % 4 == 0;
+    size_t total = (size_t)n * (vec ? dm / 4 : dm);
+    unsigned grid = (unsigned)((total + 255) / 256);
+#define JB_SC(TO, V)                                                                                  \
+    launch(short_conv_kernel<TO, V>, grid, 256, 0, st, x, w, state, (size_t)slot_stride, row_pos, row_seq, seq_slot, (TO *)out, \
+           n, dm, taps, what)
+    if (out_dt == JB_F32) {
+        if (vec) JB_SC(float, 4); else JB_SC(float, 1);
+    } else if (out_dt == JB_BF16) {
+        if (vec) JB_SC(bf16, 4); else JB_SC(bf16, 1);
+    } else {
+        return JB_EINVAL;
+    }
+#undef JB_SC
+    return launch_status();
+}
+
+// Floats of scratch for n rows cut into pieces (0 when one launch does it).
+extern "C" int jb_mingru_piece(void) { return 64; }
+extern "C" long long jb_mingru_scratch(int n, int n_seqs, int W, int every_row_starts)
+{
+    int piece = jb_mingru_piece();
+    if (every_row_starts || n <= piece)
+        return 0;
+    long long pieces = (n + piece - 1) / piece;
+    return pieces * 3 * W + (long long)n_seqs * W;
+}
+
+// P: float32 [S, n, ld]; the mixer's columns [z | x | g] start at col0.  out: [n, W] in
+// out_dt.  every_row_starts: each row is the one new token of its sequence.
+extern "C" int jb_mingru(const float *P, int S, long long stride, int ld, int col0, const float *bias,
+                         float *state, const int32_t *row_seq, const int32_t *seq_slot, float *scratch,
+                         void *out, int out_dt, int n, int n_seqs, int W, int every_row_starts,
+                         cudaStream_t st)
+{
+    if (n <= 0)
+        return JB_OK;
+    if (W <= 0 || S <= 0 || ld < col0 + 3 * W || state == nullptr || (out_dt != JB_F32 && out_dt != JB_BF16))
+        return JB_EINVAL;
+    GruIn in{P, S, (size_t)stride, ld, col0, bias, W};
+    int piece = every_row_starts ? 1 : jb_mingru_piece();
+    int pieces = (n + piece - 1) / piece;
+    dim3 grid((unsigned)((W + 127) / 128), (unsigned)pieces);
+    const float *carry = nullptr, *init = nullptr;
+    if (!every_row_starts && pieces > 1) {
+        if (scratch == nullptr)
+            return JB_EINVAL;
+        float *AB = scratch, *cr = scratch + (size_t)pieces * 2 * W, *ini = cr + (size_t)pieces * W;
+        launch(mingru_pieces_kernel, grid, 128, 0, st, in, (const float *)state, row_seq, seq_slot, AB, ini, n,
+               piece);
+        launch(mingru_carry_kernel, (unsigned)((W + 127) / 128), 128, 0, st, (const float *)AB, cr, W, pieces);
+        carry = cr;
+        init = ini;
+    }
+    if (out_dt == JB_F32)
+        launch(mingru_scan_kernel<float>, grid, 128, 0, st, in, state, row_seq, seq_slot, carry, init,
+               (float *)out, n, piece);
+    else
+        launch(mingru_scan_kernel<bf16>, grid, 128, 0, st, in, state, row_seq, seq_slot, carry, init,
+               (bf16 *)out, n, piece);
+    return launch_status();
+}

@@ -366,9 +366,120 @@ qk_norm_rope_append_row_kernel(
     }
 }
 
+
+// q, k and v out of the fused product's sums for mixers that add a bias to the
+// product, norm q and k per head, rotate only the first 2 rot_half values of a head
+// (value i with value i + rot_half) and have values of another head size than the
+// keys.  One warp per (row, head slot): the q heads, the k heads, the v heads of the
+// row [q | k | v | ...] whose length is ld.  Norm weights are float32 (null: no
+// norm), bias is float32 over the product's columns (null: none), cs / sn are
+// [positions, rot_half] (rot_half 0: no rotation).  A lane whose value turns fetches
+// its partner's sums too, so nothing crosses lanes but the sum of squares.
+template <typename TC>
+__global__ void __launch_bounds__(128)
+qkv_prepare_append_kernel(const float *__restrict__ qkv, int S, size_t split_stride, int ld,
+                          const float *__restrict__ bias, const float *__restrict__ q_w,
+                          const float *__restrict__ k_w, float eps, const float *__restrict__ cs,
+                          const float *__restrict__ sn, int rot_half,
+                          const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
+                          const int32_t *__restrict__ block_table, int bt_stride,
+                          TC *__restrict__ q_out, TC *__restrict__ k_cache, TC *__restrict__ v_cache,
+                          int n, int nh, int nkv, int hd, int vd)
+{
+    pdl_trigger();
+    unsigned slots = nh + 2 * nkv;
+    unsigned task = blockIdx.x * blockDim.y + threadIdx.y;
+    if (task >= (unsigned)n * slots)
+        return;
+    unsigned row = task / slots, hs = task - row * slots;
+    int lane = threadIdx.x;
+    bool is_q = hs < (unsigned)nh;
+    bool is_v = hs >= (unsigned)(nh + nkv);
+    int pos = row_pos[row];
+    int page = k_cache != nullptr ? block_table[(size_t)row_seq[row] * bt_stride + pos / PAGE] : 0;
+    const float *w = is_v ? nullptr : is_q ? q_w : k_w;
+    int len = is_v ? vd : hd;
+    int rot = is_v ? 0 : 2 * rot_half;
+    size_t col0 = is_q ? (size_t)hs * hd
+                       : !is_v ? (size_t)nh * hd + (size_t)(hs - nh) * hd
+                               : (size_t)(nh + nkv) * hd + (size_t)(hs - nh - nkv) * vd;
+    pdl_wait();
+    TC *dst;
+    if (is_q) {
+        dst = q_out + ((size_t)row * nh + hs) * hd;
+    } else {
+        if (k_cache == nullptr)
+            return;
+        int kvh = !is_v ? hs - nh : hs - nh - nkv;
+        size_t at = ((size_t)page * nkv + kvh) * PAGE + (pos % PAGE);
+        dst = !is_v ? k_cache + at * hd : v_cache + at * vd;
+    }
+    const float *src = qkv + (size_t)row * ld + col0;
+    const float *b = bias != nullptr ? bias + col0 : nullptr;
+    float ss = 0.0f;
+    if (w != nullptr) {
+        for (int i = lane; i < len; i += 32) {
+            float v = add_partials(b != nullptr ? b[i] : 0.0f, src + i, S, split_stride);
+            ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+    }
+    float scale = w != nullptr ? 1.0f / sqrtf(ss / (float)len + eps) : 1.0f;
+    for (int i = lane; i < len; i += 32) {
+        float v = add_partials(b != nullptr ? b[i] : 0.0f, src + i, S, split_stride);
+        if (w != nullptr)
+            v = (v * scale) * w[i];
+        if (i < rot) {
+            int j = i < rot_half ? i + rot_half : i - rot_half;
+            float u = add_partials(b != nullptr ? b[j] : 0.0f, src + j, S, split_stride);
+            if (w != nullptr)
+                u = (u * scale) * w[j];
+            int f = i < rot_half ? i : j;
+            float co = cs[(size_t)pos * rot_half + f], si = sn[(size_t)pos * rot_half + f];
+            // (a, b) -> (a cos - b sin, b cos + a sin), a the lower value of the pair
+            v = i < rot_half ? v * co - u * si : v * co + u * si;
+        }
+        dst[i] = from_f<TC>(v);
+    }
+}
+
 }  // namespace jb
 
 using namespace jb;
+
+// See qkv_prepare_append_kernel.  q_out may be null only with nh = 0; k_cache null:
+// nothing is appended (the product then holds q alone).
+extern "C" int jb_qkv_prepare_append(const float *qkv, int S, long long split_stride, int ld,
+                                     const float *bias, const float *q_w, const float *k_w, float eps,
+                                     const float *cs, const float *sn, int rot_half,
+                                     const int32_t *row_pos, const int32_t *row_seq,
+                                     const int32_t *block_table, int bt_stride, void *q_out,
+                                     void *k_cache, void *v_cache, int cache_dt, int n, int nh,
+                                     int nkv, int hd, int vd, cudaStream_t st)
+{
+    if (n <= 0)
+        return JB_OK;
+    if (hd <= 0 || hd > 512 || vd <= 0 || vd > 512 || rot_half < 0 || 2 * rot_half > hd || nh < 0 || nkv < 0 ||
+        (q_w == nullptr) != (k_w == nullptr) || (rot_half > 0 && (cs == nullptr || sn == nullptr)) ||
+        ld < nh * hd + (k_cache != nullptr ? nkv * (hd + vd) : 0) || (k_cache != nullptr && v_cache == nullptr))
+        return JB_EINVAL;
+    size_t tasks = (size_t)n * (nh + 2 * nkv);
+    if (tasks > 0xffffffffu)
+        return JB_EINVAL;
+    unsigned grid = (unsigned)((tasks + 3) / 4);
+    dim3 block(32, 4);
+    if (cache_dt == JB_F32)
+        launch(qkv_prepare_append_kernel<float>, grid, block, 0, st, qkv, S, (size_t)split_stride, ld, bias,
+               q_w, k_w, eps, cs, sn, rot_half, row_pos, row_seq, block_table, bt_stride, (float *)q_out,
+               (float *)k_cache, (float *)v_cache, n, nh, nkv, hd, vd);
+    else if (cache_dt == JB_BF16)
+        launch(qkv_prepare_append_kernel<bf16>, grid, block, 0, st, qkv, S, (size_t)split_stride, ld, bias,
+               q_w, k_w, eps, cs, sn, rot_half, row_pos, row_seq, block_table, bt_stride, (bf16 *)q_out,
+               (bf16 *)k_cache, (bf16 *)v_cache, n, nh, nkv, hd, vd);
+    else
+        return JB_EINVAL;
+    return launch_status();
+}
 
 extern "C" int jb_rope_table(float *cs, float *sn, const float *inv_freq, int n_pos, int half,
                              cudaStream_t st)

@@ -31,7 +31,8 @@ Engine::Engine(std::unique_ptr<Device> d, std::unique_ptr<DecoderModel> m, long 
     if (max_tokens <= 0) fail(JB_LLM_EINVAL, "max_tokens must be positive");
     if (max_seqs <= 0) max_seqs = (int)std::max(1ll, std::min(256ll, (max_tokens + 63) / 64));
     dev->make_current();
-    cache.reset(new Cache(model->kv_specs(), model->state_specs(), max_tokens, max_seqs, dtype, dev.get()));
+    cache.reset(new Cache(model->kv_specs(), model->state_specs(), max_tokens, max_seqs, dtype, dev.get(),
+                          model->block_state_specs()));
     max_positions = std::min(model->spec.max_positions, cache->max_tokens);
     model->prepare(max_positions);
     const char *env = getenv("JANAS_B200_GRAPHS");
@@ -154,6 +155,11 @@ std::vector<LayerCache> Engine::layer_caches(
         if (st != cache->mixer_state.end()) {
             lc.state = st->second.ptr;
             lc.state_spec = cache->state_spec[(int)e];
+        }
+        auto bst = cache->block_state.find((int)e);
+        if (bst != cache->block_state.end()) {
+            lc.block_state = bst->second.ptr;
+            lc.block_state_spec = cache->block_state_spec[(int)e];
         }
         lc.n_slots = cache->max_seqs;
         int src = cache_entry_[e];

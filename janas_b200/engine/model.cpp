@@ -33,7 +33,7 @@ TensorList DecoderModel::layer_tensors(int i) const {
     layer_names(i, n);
     TensorList t;
     const Block &b = *blocks[(size_t)i];
-    b.mixer_norm->tensors(n[2], t);
+    if (b.mixer_norm) b.mixer_norm->tensors(n[2], t);
     b.mixer->tensors(n[0], t);
     if (b.post_mixer_norm) b.post_mixer_norm->tensors(n[4], t);
     if (b.ffn_norm) b.ffn_norm->tensors(n[3], t);
@@ -96,7 +96,7 @@ void DecoderModel::load_layer(int i, TensorMap &t) {
     std::string n[6];
     layer_names(i, n);
     Block &b = *blocks[(size_t)i];
-    b.mixer_norm->load(n[2], t);
+    if (b.mixer_norm) b.mixer_norm->load(n[2], t);
     b.mixer->load(n[0], t);
     if (b.post_mixer_norm) b.post_mixer_norm->load(n[4], t);
     if (b.ffn_norm) b.ffn_norm->load(n[3], t);
@@ -154,8 +154,9 @@ size_t DecoderModel::weight_bytes() const {
     for (auto &e : spec.run_order) used.insert(e.layer);
     for (int layer : used) {
         const Block &b = *blocks[(size_t)layer];
-        total += b.mixer->weight_bytes() + b.mixer_norm->weight_bytes() + b.weight_bytes();
-        for (const Part *p : {(const Part *)b.feed_forward.get(), (const Part *)b.ffn_norm.get(),
+        total += b.mixer->weight_bytes() + b.weight_bytes();
+        for (const Part *p : {(const Part *)b.mixer_norm.get(), (const Part *)b.feed_forward.get(),
+                              (const Part *)b.ffn_norm.get(),
                               (const Part *)b.post_mixer_norm.get(), (const Part *)b.post_ffn_norm.get()})
             if (p) total += p->weight_bytes();
     }
@@ -175,19 +176,26 @@ std::vector<StateSpec> DecoderModel::state_specs() const {
     return out;
 }
 
+std::vector<StateSpec> DecoderModel::block_state_specs() const {
+    std::vector<StateSpec> out;
+    for (auto &e : spec.run_order) out.push_back(blocks[(size_t)e.layer]->state_spec());
+    return out;
+}
+
 void DecoderModel::prepare(long long n_positions) {
     for (auto &b : blocks) b->mixer->prepare(n_positions);
 }
 
 bool DecoderModel::supports(StepKind kind) const {
     for (auto &b : blocks)
-        if (!b->mixer->supports(kind)) return false;
+        if (!b->mixer->supports(kind) || !b->supports(kind)) return false;
     return true;
 }
 
 bool DecoderModel::graph_safe() const {
     for (auto &b : blocks)
-        if (!b->mixer->graph_safe() || (b->feed_forward && !b->feed_forward->graph_safe())) return false;
+        if (!b->mixer->graph_safe() || (b->feed_forward && !b->feed_forward->graph_safe()) || !b->graph_safe())
+            return false;
     return true;
 }
 
@@ -200,6 +208,7 @@ Buf DecoderModel::forward(StepContext &ctx, const int32_t *tokens, std::vector<L
         fail(JB_LLM_EINVAL, fmt("position %lld is beyond the %lld learned position vectors", ctx.max_pos,
                                 position_table.shape.at(0)));
     Buf x = ops::embed(d, embedding, tokens, n, position_table ? &position_table : nullptr, ctx.row_pos);
+    if (spec.embedding_scale != 1.0) ops::scale_(d, x.as<float>(), n * spec.hidden_size, (float)spec.embedding_scale);
     Stack pending;
     ctx.normed.reset();
     ctx.normed_by = nullptr;

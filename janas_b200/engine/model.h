@@ -46,6 +46,7 @@ public:
 
     std::vector<KVSpec> kv_specs() const;         // per run-order entry
     std::vector<StateSpec> state_specs() const;
+    std::vector<StateSpec> block_state_specs() const;
     void prepare(long long n_positions);
     bool supports(StepKind kind) const;
     bool graph_safe() const;

@@ -180,13 +180,23 @@ private:
 // with slope_a = 2^(-e (a + 1) / H) for head a of H (distance_slope_exponent = e); a
 // query temperature, q_i multiplied by 1 + coef * ln(floor((i + 1) / every) + 1).
 //
+// Also optional: an RMS norm of q and of k per head (one weight vector each for all
+// heads, before any rotation); a rotation of the first rotary_dim values of each q and k
+// head with the position (a `position` part of kind rope_neox: value i turns with value
+// i + rotary_dim / 2, the rest of the head passes unchanged); first positions that stay
+// visible beside the window, j < keep_first, at their true positions; and weights that
+// are no softmax: with score_bias the weight of a visible key is
+// sigmoid(s_ij + score_bias_a), a learned number per head, not normalized over the keys.
+//
 // params: hidden_size, num_heads, num_kv_heads, head_dim, v_head_dim (default: head_dim),
-// scale (default 1/sqrt(head_dim)), window (0: none), softcap (0 or absent: none),
+// scale (default 1/sqrt(head_dim)), window (0: none), keep_first (0: none), qk_norm_eps
+// (absent: no q/k norm), position (a part; absent: none), score_bias (boolean),
+// softcap (0 or absent: none),
 // distance_slope_exponent (absent: no bias), q_temp_coef and q_temp_every (absent or
-// every = 0: none), bias, head_scale, sink, own_kv
+// every = 0: none), bias (on q, k, v), out_bias (on o; default: as bias), head_scale, sink, own_kv
 // (booleans; own_kv false: the run order gives this layer another entry's cache and it
 // has no key and value products), names (optional): q, k, v, o, bias (a suffix),
-// head_scale, sink.
+// head_scale, sink, q_norm, k_norm, score_bias.
 class SinkAttention : public Mixer {
 public:
     SinkAttention(const PartSpec &s, DType dt, Device *d) : Mixer(s, dt, d) {
@@ -198,6 +208,7 @@ public:
         g_.window = (int)s.get_int("window", 0);
         g_.scale = s.has("scale") ? (float)s.get_double("scale") : (float)(1.0 / std::sqrt((double)g_.hd));
         bias_ = flag(s, "bias", false);
+        out_bias_ = flag(s, "out_bias", bias_);
         head_scale_ = flag(s, "head_scale", false);
         sink_ = flag(s, "sink", false);
         own_kv_ = flag(s, "own_kv", true);
@@ -213,10 +224,31 @@ public:
         if (g_.hd <= 0 || g_.hd > 512 || g_.vd <= 0 || g_.vd > 512)
             config_error(fmt("sink_attention: head sizes %d and %d: the kernels take 1 to 512", g_.hd, g_.vd));
         if (g_.window < 0) config_error("sink_attention: window must not be negative");
+        g_.keep_first = g_.window > 0 ? (int)s.get_int("keep_first", 0) : 0;
+        if (g_.keep_first < 0) config_error("sink_attention: keep_first must not be negative");
+        qk_norm_ = s.has("qk_norm_eps");
+        qk_eps_ = qk_norm_ ? (float)s.get_double("qk_norm_eps") : 0.0f;
+        score_bias_ = flag(s, "score_bias", false);
+        if (score_bias_ && (sink_ || g_.softcap > 0.0f || has_slopes_ || head_scale_))
+            config_error("sink_attention: weights that are sigmoids take no sink, cap, slopes or head factors");
+        if (s.has("position")) {
+            position_ = build_position(s.get_part("position"), dt, d);
+            if (position_->rotary_dim() > g_.hd)
+                config_error(fmt("sink_attention: rotary_dim %d is above the head size %d", position_->rotary_dim(),
+                                 g_.hd));
+        }
+        prepared_ = qk_norm_ || (position_ && position_->rotary_dim() > 0);
+        if (prepared_ && q_every_ > 0)
+            config_error("sink_attention: a query temperature together with a q/k norm or a rotation is not built");
+        if (prepared_ && !own_kv_)
+            config_error("sink_attention: a q/k norm or a rotation needs keys and values of the layer's own");
         const Json &nm = s.params.get("names");
         auto leaf = [&](const char *key, const char *dflt) {
             return nm.is_object() && nm.get(key).is_string() ? nm.get(key).as_string() : std::string(dflt);
         };
+        n_qn_ = leaf("q_norm", "q_norm.weight");
+        n_kn_ = leaf("k_norm", "k_norm.weight");
+        n_sb_ = leaf("score_bias", "score_bias");
         n_q_ = leaf("q", "q_proj.weight");
         n_k_ = leaf("k", "k_proj.weight");
         n_v_ = leaf("v", "v_proj.weight");
@@ -229,18 +261,24 @@ public:
     void tensors(const std::string &p, TensorList &out) const override {
         long long qw = (long long)g_.nh * g_.hd, kw = (long long)g_.nkv * g_.hd, vw = (long long)g_.nkv * g_.vd;
         long long ow = (long long)g_.nh * g_.vd;
-        auto mat = [&](const std::string &leaf, long long rows, long long cols) {
+        auto mat = [&](const std::string &leaf, long long rows, long long cols, bool with_bias) {
             out.emplace_back(name(p, leaf), TensorSpec{{rows, cols}, MATRIX, false});
-            if (bias_) out.emplace_back(name(p, leaf + n_bias_), TensorSpec{{rows}, PARAM, false, 0.0f, 0.02f});
+            if (with_bias) out.emplace_back(name(p, leaf + n_bias_), TensorSpec{{rows}, PARAM, false, 0.0f, 0.02f});
         };
-        mat(n_q_, qw, hidden_);
+        mat(n_q_, qw, hidden_, bias_);
         if (own_kv_) {
-            mat(n_k_, kw, hidden_);
-            mat(n_v_, vw, hidden_);
+            mat(n_k_, kw, hidden_, bias_);
+            mat(n_v_, vw, hidden_, bias_);
         }
         if (head_scale_) out.emplace_back(name(p, n_hs_), TensorSpec{{g_.nh}, PARAM, false, 1.0f, 0.1f});
         if (sink_) out.emplace_back(name(p, n_sink_), TensorSpec{{g_.nh}, PARAM, false, 0.0f, 0.5f});
-        mat(n_o_, hidden_, ow);
+        if (qk_norm_) {
+            out.emplace_back(name(p, n_qn_), TensorSpec{{g_.hd}, PARAM, false, 1.0f, 0.1f});
+            out.emplace_back(name(p, n_kn_), TensorSpec{{g_.hd}, PARAM, false, 1.0f, 0.1f});
+        }
+        if (score_bias_) out.emplace_back(name(p, n_sb_), TensorSpec{{g_.nh}, PARAM, false, -2.0f, 0.5f});
+        mat(n_o_, hidden_, ow, out_bias_);
+        if (position_) position_->tensors(name(p, "position"), out);
     }
 
     void load(const std::string &p, TensorMap &t) override {
@@ -261,8 +299,17 @@ public:
         }
         if (head_scale_) temp_ = take(t, name(p, n_hs_));
         if (sink_) sinks_ = take(t, name(p, n_sink_));
+        if (qk_norm_) {
+            q_norm_ = take(t, name(p, n_qn_));
+            k_norm_ = take(t, name(p, n_kn_));
+        }
+        if (score_bias_) {
+            score_b_ = take(t, name(p, n_sb_));
+            g_.score_bias = (const float *)score_b_.ptr;
+        }
+        if (position_) position_->load(name(p, "position"), t);
         w_o_ = take(t, name(p, n_o_));
-        if (bias_) b_o_ = take(t, name(p, n_o_ + n_bias_));
+        if (out_bias_) b_o_ = take(t, name(p, n_o_ + n_bias_));
         if (has_slopes_) {
             std::vector<float> sl((size_t)g_.nh);
             for (int a = 0; a < g_.nh; a++)
@@ -285,11 +332,12 @@ public:
     }
 
     size_t weight_bytes() const override {
-        return w_in_.bytes() + w_o_.bytes() + b_in_.bytes() + b_o_.bytes() + temp_.bytes() + sinks_.bytes();
+        return w_in_.bytes() + w_o_.bytes() + b_in_.bytes() + b_o_.bytes() + temp_.bytes() + sinks_.bytes() +
+               q_norm_.bytes() + k_norm_.bytes() + score_b_.bytes();
     }
 
     KVSpec kv_spec() const override {
-        return own_kv_ ? KVSpec{g_.nkv, g_.hd, g_.window, g_.vd} : KVSpec();
+        return own_kv_ ? KVSpec{g_.nkv, g_.hd, g_.window, g_.vd, false, g_.keep_first} : KVSpec();
     }
 
     bool take_side_rows(DevTensor &m) override {
@@ -303,13 +351,19 @@ public:
         return true;
     }
 
-    void prepare(long long) override { chunk_ = ops::attention_chunk(); }
+    void prepare(long long n_positions) override {
+        chunk_ = ops::attention_chunk();
+        if (position_) position_->prepare(n_positions);
+    }
     bool supports(StepKind) const override { return true; }
     bool graph_safe() const override { return true; }
 
     Stack forward(StepContext &ctx, const void *h, LayerCache &cache) override {
         Device &d = *ctx.dev;
         if (!chunk_) chunk_ = ops::attention_chunk();
+        if (position_ && ctx.max_pos >= position_->n_positions())
+            fail(JB_LLM_EINVAL, fmt("position %lld is beyond the %lld positions the encoding was prepared "
+                                    "for", ctx.max_pos, position_->n_positions()));
         if (!cache.kv.k || cache.kv_heads != g_.nkv || cache.head_dim != g_.hd || cache.v_head_dim != g_.vd)
             fail(JB_LLM_EINVAL, "sink_attention: the cache this layer was given does not hold keys and values "
                                 "of its head count and sizes");
@@ -323,8 +377,24 @@ public:
         Stack qkv = ops::linear(d, h, ctx.dtype, n, hidden_, w_in_);
         int max_chunks = (int)(ctx.max_pos / chunk_ + 1);
         if (g_.window) max_chunks = std::min(max_chunks, (g_.window - 1) / chunk_ + 2);
+        // the kept first positions' chunks come in front of the window's
+        max_chunks += ops::attention_kept_chunks(g_.window, g_.keep_first);
         bool decode = ctx.kind == DECODE;
-        if (decode && ctx.dtype == BF16 && q_every_ == 0) {
+        if (prepared_) {
+            // bias, per-head norms and the rotation in one pass over the product's sums, K and V
+            // into the cache; then attention over the cache
+            int rot = position_ ? position_->rotary_dim() : 0;
+            Buf q = ops::qkv_prepare_append(d, qkv, b_in, qk_norm_ ? (const float *)q_norm_.ptr : nullptr,
+                                            qk_norm_ ? (const float *)k_norm_.ptr : nullptr, qk_eps_,
+                                            rot ? position_->cos() : nullptr, rot ? position_->sin() : nullptr,
+                                            rot / 2, ctx.row_pos, ctx.row_seq, cache.kv, g_, ctx.dtype);
+            keep_side(ctx, qkv);
+            const int32_t *blocks = prefill_blocks(ctx, decode);
+            Buf a = ops::attention(d, q.ptr, n, cache.kv, g_, ctx.row_pos, ctx.row_seq, max_chunks, blocks,
+                                   n_blocks_, decode);
+            return output(ctx, a);
+        }
+        if (decode && ctx.dtype == BF16 && q_every_ == 0 && !g_.keep_first && !score_bias_) {
             // one new token per sequence: the attention kernel makes q and the new key and
             // value from the product's sums and its bias itself, where it takes the sizes
             Buf a = ops::attention_decode_qkv(d, qkv, nullptr, nullptr, 0.0f, nullptr, nullptr, cache.kv, g_,
@@ -337,25 +407,31 @@ public:
         Buf q = ops::qkv_bias_append(d, qkv, b_in, ctx.row_pos, ctx.row_seq, cache.kv, g_, ctx.dtype, own_kv_,
                                      q_coef_, q_every_);
         keep_side(ctx, qkv);
-        const int32_t *blocks = nullptr;
-        int n_blocks = 0;
-        if (!decode && ctx.dtype == BF16 && ops::attention_tc_ok(g_.nh, g_.nkv, g_.hd) && g_.vd == g_.hd &&
-            (!head_scale_ || g_.head_scale_positive) && !ctx.seq_len.empty()) {
-            int per = ops::attention_block_positions(g_.nh, g_.nkv);
-            std::string key = "attention_blocks/" + std::to_string(per);
-            auto it = ctx.extras.find(key);
-            if (it == ctx.extras.end()) {
-                StepContext::Extra e;
-                e.buf = ops::attention_blocks(d, ctx.seq_row0.data(), ctx.seq_pos0.data(), ctx.seq_len.data(),
-                                              ctx.n_seqs, per, &e.n);
-                it = ctx.extras.emplace(key, std::move(e)).first;
-            }
-            blocks = it->second.buf.as<int32_t>();
-            n_blocks = it->second.n;
-        }
-        Buf a = ops::attention(d, q.ptr, n, cache.kv, g_, ctx.row_pos, ctx.row_seq, max_chunks, blocks, n_blocks,
+        const int32_t *blocks = prefill_blocks(ctx, decode);
+        Buf a = ops::attention(d, q.ptr, n, cache.kv, g_, ctx.row_pos, ctx.row_seq, max_chunks, blocks, n_blocks_,
                                decode);
         return output(ctx, a);
+    }
+
+    // Runs of consecutive positions for the tensor-core prefill kernel, where it takes this
+    // mixer (null otherwise); the same for every layer of the step with this grouping of
+    // heads.  n_blocks_ gets their number.
+    const int32_t *prefill_blocks(StepContext &ctx, bool decode) {
+        n_blocks_ = 0;
+        if (decode || ctx.dtype != BF16 || !ops::attention_tc_ok(g_.nh, g_.nkv, g_.hd) || g_.vd != g_.hd ||
+            (head_scale_ && !g_.head_scale_positive) || g_.keep_first || score_bias_ || ctx.seq_len.empty())
+            return nullptr;
+        int per = ops::attention_block_positions(g_.nh, g_.nkv);
+        std::string key = "attention_blocks/" + std::to_string(per);
+        auto it = ctx.extras.find(key);
+        if (it == ctx.extras.end()) {
+            StepContext::Extra e;
+            e.buf = ops::attention_blocks(*ctx.dev, ctx.seq_row0.data(), ctx.seq_pos0.data(), ctx.seq_len.data(),
+                                          ctx.n_seqs, per, &e.n);
+            it = ctx.extras.emplace(key, std::move(e)).first;
+        }
+        n_blocks_ = it->second.n;
+        return it->second.buf.as<int32_t>();
     }
 
     // the product goes to whoever gave the side rows, or back to the pool
@@ -369,7 +445,7 @@ public:
 
     Stack output(StepContext &ctx, const Buf &a) {
         Stack out = ops::linear(*ctx.dev, a.ptr, ctx.dtype, ctx.n_rows, (long long)g_.nh * g_.vd, w_o_);
-        out.bias = bias_ ? (const float *)b_o_.ptr : nullptr;
+        out.bias = out_bias_ ? (const float *)b_o_.ptr : nullptr;
         return out;
     }
 
@@ -386,7 +462,14 @@ private:
     }
     long long hidden_;
     ops::AttnGeometry g_;
-    bool bias_, head_scale_, sink_, own_kv_;
+    bool bias_, out_bias_, head_scale_, sink_, own_kv_;
+    bool qk_norm_ = false, score_bias_ = false;
+    bool prepared_ = false;      // q and k are normed or rotated: qkv_prepare_append makes them
+    float qk_eps_ = 0.0f;
+    std::unique_ptr<PositionEncoding> position_;
+    DevTensor q_norm_, k_norm_, score_b_;
+    std::string n_qn_, n_kn_, n_sb_;
+    int n_blocks_ = 0;
     bool has_slopes_ = false;
     double slope_exponent_ = 0.0;
     float q_coef_ = 0.0f;

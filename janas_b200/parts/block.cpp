@@ -10,6 +10,13 @@
 // sublayer's result, computed from the sublayer's own input:
 //     h = norm_in(x);  y = sublayer(h);  y *= sigmoid(G h + g);  x += norm_out(y)
 // for the mixer and then, where the layer has one, for the feed-forward.
+//
+// result_norm: no norm in front of a sublayer, one on its result alone; the sublayers read
+// the residual stream itself, optionally through a short causal convolution over time on
+// every channel (weights [hidden, taps], no bias):
+//     h = x + conv(x);  x += norm(sublayer(h))          conv(x)_t = sum_j w[:, j] x_{t - taps + 1 + j}
+// for the mixer and then, where the layer has one, for the feed-forward.  The last
+// taps - 1 inputs of either convolution are state of the sequence (float32, per slot).
 #include "part.h"
 
 namespace jb {
@@ -19,6 +26,7 @@ namespace {
 class PreNormBlock : public Block {
 public:
     explicit PreNormBlock(BlockParts p) : Block(std::move(p)) {
+        if (!mixer_norm) config_error("prenorm: the layer needs a norm in front of its mixer");
         if (!feed_forward || !ffn_norm) config_error("prenorm: the layer needs a feed-forward and its norm");
         if (post_mixer_norm || post_ffn_norm) config_error("prenorm: the arrangement has no norms on results");
     }
@@ -38,6 +46,7 @@ public:
 class ParallelBlock : public Block {
 public:
     ParallelBlock(BlockParts p, const LayerSpec &ls) : Block(std::move(p)) {
+        if (!mixer_norm) config_error("parallel: the layer needs its norm");
         if (ffn_norm || post_mixer_norm || post_ffn_norm)
             config_error("parallel: the arrangement has one norm, before both sublayers");
         const Json &m = ls.block_params.get("residual_mult");
@@ -79,6 +88,7 @@ private:
 class SandwichBlock : public Block {
 public:
     SandwichBlock(BlockParts p, const LayerSpec &ls, DType dt, Device *d) : Block(std::move(p)), dev_(d) {
+        if (!mixer_norm) config_error("sandwich: the mixer needs a norm in front of it");
         if (!post_mixer_norm || (feed_forward && !post_ffn_norm))
             config_error("sandwich: every sublayer needs a norm on its result");
         if (feed_forward && !ffn_norm) config_error("sandwich: the feed-forward needs its norm");
@@ -223,9 +233,122 @@ private:
     std::vector<std::pair<std::string, std::vector<long long>>> unused_;
 };
 
+// block_params: hidden_size; conv_taps (0 or absent: the sublayers read x as it is);
+// mixer_conv / ffn_conv: the tensor names (below the layer's prefix) of the convolutions'
+// weights.  The norms are the layer's post_mixer_norm and post_ffn_norm; it has no others.
+class ResultNormBlock : public Block {
+public:
+    ResultNormBlock(BlockParts p, const LayerSpec &ls) : Block(std::move(p)) {
+        if (mixer_norm || ffn_norm) config_error("result_norm: the arrangement has no norm in front of a sublayer");
+        if (!post_mixer_norm || (feed_forward && !post_ffn_norm))
+            config_error("result_norm: every sublayer needs a norm on its result");
+        const Json &bp = ls.block_params;
+        hidden_ = bp.get("hidden_size").is_number() ? bp.get("hidden_size").as_int() : post_mixer_norm->size();
+        taps_ = bp.get("conv_taps").is_number() ? (int)bp.get("conv_taps").as_int() : 0;
+        if (taps_ < 0) config_error("result_norm: conv_taps must not be negative");
+        conv_name_[0] = bp.get("mixer_conv").is_string() ? bp.get("mixer_conv").as_string() : "mixer_conv";
+        conv_name_[1] = bp.get("ffn_conv").is_string() ? bp.get("ffn_conv").as_string() : "ffn_conv";
+        n_sub_ = feed_forward ? 2 : 1;
+    }
+
+    void tensors(const std::string &prefix, TensorList &out) const override {
+        if (!taps_) return;
+        for (int i = 0; i < n_sub_; i++)
+            out.emplace_back(Part::name(prefix, conv_name_[i]), TensorSpec{{hidden_, taps_}, PARAM, false, 0.0f, 0.2f});
+    }
+
+    void load(const std::string &prefix, TensorMap &t) override {
+        if (!taps_) return;
+        for (int i = 0; i < n_sub_; i++) conv_[i] = Part::take(t, Part::name(prefix, conv_name_[i]));
+    }
+
+    size_t weight_bytes() const override { return conv_[0].bytes() + conv_[1].bytes(); }
+
+    // the last taps - 1 inputs of each sublayer's convolution
+    StateSpec state_spec() const override {
+        if (taps_ < 2) return StateSpec();
+        return StateSpec{{n_sub_, taps_ - 1, hidden_}, F32};
+    }
+
+    void forward(StepContext &ctx, float *x, Stack &pending, LayerCache &cache) override {
+        Device &d = *ctx.dev;
+        long long n = ctx.n_rows;
+        ctx.normed.reset();
+        ctx.normed_by = nullptr;
+        if (pending) {
+            ops::add_(d, x, n, hidden_, pending);
+            pending = Stack();
+        }
+        if (taps_ >= 2 && (!cache.block_state || cache.block_state_spec.bytes() != state_spec().bytes()))
+            fail(JB_LLM_EINVAL, "result_norm: the cache holds no state for the layer's convolutions");
+        bool few = ctx.kind == DECODE && ctx.dtype == BF16;
+        for (int i = 0; i < n_sub_; i++) {
+            Buf h = read(ctx, x, i, cache);
+            Stack y = i == 0 ? mixer->forward(ctx, h ? h.ptr : x, cache)
+                             : feed_forward->forward(ctx, h ? h.ptr : x);
+            Norm *post = i == 0 ? post_mixer_norm.get() : post_ffn_norm.get();
+            ops::LnParams lp;
+            bool rms = false;
+            if (post->layer_norm(&lp, &rms)) {
+                ops::norm_residual_(d, x, y, lp, rms, few);
+            } else {
+                // any other norm: the result summed, normed, added
+                Buf t = d.pool.get((size_t)n * (size_t)hidden_ * 4);
+                cuda_check(cudaMemsetAsync(t.ptr, 0, t.bytes, d.stream), "clearing a sum");
+                ops::add_(d, t.as<float>(), n, hidden_, y);
+                Stack one;
+                one.buf = post->apply(ctx, t.as<float>(), n, F32, nullptr, nullptr, 0);
+                one.S = 1;
+                one.n = n;
+                one.m = hidden_;
+                ops::add_(d, x, n, hidden_, one);
+            }
+        }
+    }
+
+private:
+    // what sublayer i reads: x through its convolution in the compute type (an empty
+    // handle: x itself, float32 compute and no convolution)
+    Buf read(StepContext &ctx, float *x, int i, LayerCache &cache) {
+        Device &d = *ctx.dev;
+        long long n = ctx.n_rows;
+        if (!taps_) {
+            if (ctx.dtype == F32) return Buf();
+            Buf h = d.pool.get((size_t)n * (size_t)hidden_ * dtype_size(ctx.dtype));
+            if (jb_convert(x, F32, h.ptr, ctx.dtype, n * hidden_, d.stream) != 0)
+                fail(JB_LLM_EFAIL, "result_norm: the conversion could not be launched");
+            return h;
+        }
+        float *st = taps_ >= 2 ? (float *)cache.block_state + (size_t)i * (size_t)(taps_ - 1) * (size_t)hidden_
+                               : nullptr;
+        // A slot's state is [n_sub, taps - 1, hidden]: the kernel takes the stride between
+        // slots from the sublayers' count.
+        const float *w = (const float *)conv_[i].ptr;
+        long long slot_stride = (long long)n_sub_ * (taps_ - 1) * hidden_;
+        if (ctx.kind == EXTEND && taps_ >= 2) {
+            // rows read inputs of earlier steps that other rows of this step replace: two launches
+            Buf h = ops::short_conv(d, x, n, hidden_, w, taps_, st, slot_stride, ctx.row_pos, ctx.row_seq,
+                                    ctx.seq_slot, ctx.dtype, true, false);
+            ops::short_conv(d, x, n, hidden_, w, taps_, st, slot_stride, ctx.row_pos, ctx.row_seq, ctx.seq_slot,
+                            ctx.dtype, false, true);
+            return h;
+        }
+        return ops::short_conv(d, x, n, hidden_, w, taps_, st, slot_stride, ctx.row_pos, ctx.row_seq, ctx.seq_slot,
+                               ctx.dtype, true, taps_ >= 2);
+    }
+
+    long long hidden_ = 0;
+    int taps_ = 0, n_sub_ = 1;
+    std::string conv_name_[2];
+    DevTensor conv_[2];
+};
+
 }  // namespace
 
 void register_builtin_blocks() {
+    register_block("result_norm", [](BlockParts p, const LayerSpec &ls, DType, Device *) {
+        return std::unique_ptr<Block>(new ResultNormBlock(std::move(p), ls));
+    });
     register_block("prenorm", [](BlockParts p, const LayerSpec &, DType, Device *) {
         return std::unique_ptr<Block>(new PreNormBlock(std::move(p)));
     });

@@ -150,6 +150,12 @@ public:
         return ops::layernorm(*ctx.dev, x, n, size_, params(), out_dt, &a, b, mult, nullptr, 0);
     }
 
+    bool layer_norm(ops::LnParams *out, bool *rms) const override {
+        *out = params();
+        *rms = false;
+        return true;
+    }
+
     long long size() const override { return size_; }
 
     Json info() const override {

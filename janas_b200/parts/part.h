@@ -47,6 +47,8 @@ struct LayerCache {
     int kv_heads = 0, head_dim = 0, v_head_dim = 0;
     void *state = nullptr;              // [slots, *state shape], indexed by slot; or null
     StateSpec state_spec;
+    void *block_state = nullptr;        // the block arrangement's own state, [slots, *shape]; or null
+    StateSpec block_state_spec;
     int n_slots = 0;
 };
 
@@ -142,6 +144,10 @@ public:
     // its parameters, so that a block can take it into the kernel that ends a
     // sublayer; every other norm answers false.
     virtual bool dynamic_tanh(ops::DytParams *out) const { return false; }
+    // A norm that is (v - mean) / sqrt(var + eps) * w + b with float32 parameters gives them
+    // here (rms: no mean is taken off), so that a block can take it into the kernel that
+    // norms a sublayer's result and adds it to the residual stream; the others answer false.
+    virtual bool layer_norm(ops::LnParams *out, bool *rms) const { return false; }
 };
 
 class PositionEncoding : public Part {
@@ -203,6 +209,12 @@ public:
     virtual void tensors(const std::string &prefix, TensorList &out) const {}
     virtual void load(const std::string &prefix, TensorMap &t) {}
     virtual size_t weight_bytes() const { return 0; }
+    // Fixed-size state per sequence that the arrangement itself keeps (none() for
+    // nothing), beside its mixer's; it arrives in LayerCache::block_state.
+    virtual StateSpec state_spec() const { return StateSpec(); }
+    // as Mixer::supports and Mixer::graph_safe, for what the arrangement itself does
+    virtual bool supports(StepKind) const { return true; }
+    virtual bool graph_safe() const { return true; }
     // The norm the NEXT thing applies to the residual stream after this layer
     // (the next layer's first norm, or the model's last one), or null; a block may
     // compute it together with its own last step and leave the result in
@@ -240,6 +252,8 @@ std::unique_ptr<Block> build_block(const LayerSpec &ls, DType dt, Device *dev);
 // gate, up as one: src/llm/model_attn.c:255, src/llm/model_ffn.c:349).  If their
 // dtypes differ, the widest is taken.  The sources are released as they are copied.
 DevTensor fuse_rows(Device &dev, std::vector<DevTensor> &mats);
+// The same along the columns: matrices with equally many rows side by side.
+DevTensor fuse_cols(Device &dev, std::vector<DevTensor> &mats);
 
 // the built-in kinds (each file registers its own)
 void register_builtin_norms();
@@ -247,6 +261,8 @@ void register_builtin_positions();
 void register_builtin_mixers();
 void register_builtin_feed_forwards();
 void register_builtin_blocks();
+void register_recurrent_mixers();
+void register_routed_feed_forwards();
 
 }  // namespace jb
 

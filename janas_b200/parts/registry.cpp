@@ -27,6 +27,8 @@ Tables &ready() {
         register_builtin_mixers();
         register_builtin_feed_forwards();
         register_builtin_blocks();
+        register_recurrent_mixers();
+        register_routed_feed_forwards();
     });
     return raw();
 }
@@ -116,7 +118,8 @@ std::unique_ptr<Block> build_block(const LayerSpec &ls, DType dt, Device *dev) {
     }
     BlockParts p;
     p.mixer = build_mixer(ls.mixer, dt, dev);
-    p.mixer_norm = build_norm(ls.mixer_norm, dt, dev);
+    // an arrangement whose sublayers read the residual stream itself names no mixer_norm
+    if (!ls.mixer_norm.kind.empty()) p.mixer_norm = build_norm(ls.mixer_norm, dt, dev);
     if (!ls.feed_forward.kind.empty()) {
         p.feed_forward = build_feed_forward(ls.feed_forward, dt, dev);
         // an arrangement whose sublayers share one norm names no ffn_norm
@@ -154,6 +157,38 @@ DevTensor fuse_rows(Device &dev, std::vector<DevTensor> &mats) {
         at += (size_t)m.numel() * dtype_size(dt);
     }
     dev.sync();      // the sources are freed when the caller lets go of them
+    for (auto &m : mats) m = DevTensor();
+    return out;
+}
+
+// Several matrices with equally many rows as one, columns one after the other (the down
+// matrices of a routed feed-forward's experts: one product over all experts' values).
+DevTensor fuse_cols(Device &dev, std::vector<DevTensor> &mats) {
+    if (mats.empty()) fail(JB_LLM_EINVAL, "fuse_cols: nothing to fuse");
+    if (mats.size() == 1) return mats[0];
+    DType dt = mats[0].dt;
+    long long rows = mats[0].shape.at(0), cols = 0;
+    for (auto &m : mats) {
+        if (m.dt == F32) dt = F32;
+        if (m.shape.size() != 2 || m.shape[0] != rows) fail(JB_LLM_EINVAL, "fuse_cols: columns of unequal length");
+        cols += m.shape[1];
+    }
+    dev.make_current();
+    DevTensor out = dev.tensor(dt, {rows, cols});
+    size_t es = dtype_size(dt), at = 0;
+    for (auto &m : mats) {
+        DevTensor src = m;
+        if (m.dt != dt) {
+            src = dev.tensor(dt, m.shape);
+            if (jb_convert(m.ptr, m.dt, src.ptr, dt, m.numel(), dev.stream) != 0)
+                fail(JB_LLM_EFAIL, "fuse_cols: the conversion could not be launched");
+        }
+        size_t w = (size_t)m.shape[1] * es;
+        cuda_check(cudaMemcpy2DAsync((char *)out.ptr + at, (size_t)cols * es, src.ptr, w, w, (size_t)rows,
+                                     cudaMemcpyDeviceToDevice, dev.stream), "fuse_cols: placing a matrix");
+        dev.sync();
+        at += w;
+    }
     for (auto &m : mats) m = DevTensor();
     return out;
 }
