@@ -436,6 +436,139 @@ def activation(z: torch.Tensor, kind: str, out_dtype: torch.dtype, ff: Optional[
     return out
 
 
+def attention_kept_chunks(window: int, keep_first: int) -> int:
+    """Chunks that the kept first positions of a windowed mixer add to a row's range."""
+    return int(lib().jb_attention_kept_chunks(int(window), int(keep_first)))
+
+
+def norm_residual_(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
+                   y_bias: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                   skip: Optional[torch.Tensor] = None, skip_coef: Optional[torch.Tensor] = None,
+                   rms: bool = False, few_rows: bool = False) -> torch.Tensor:
+    """x += norm(sum y + y_bias + skip_coef[:, None] * skip) * weight (+ bias), in place: a
+    layer norm (``rms``: an RMS norm) on a sublayer's result alone.  y: [S, n, dm] float32
+    partial sums; skip: [n, dm] float32 or bfloat16 with skip_coef float32 [n]."""
+    _need(x, "x", torch.float32, (None, None))
+    n, dm = x.shape
+    y = stack(y)
+    _need(y, "y", torch.float32, (None, n, dm))
+    _need(weight, "weight", torch.float32, (dm,))
+    if skip is not None:
+        _need(skip, "skip", _FLOATS, (n, dm))
+        _need(skip_coef, "skip_coef", torch.float32, (n,))
+    _check(lib().jb_norm_residual(_p(x), _p(y), y.shape[0], n * dm, _p(y_bias), _p(skip),
+                                  0 if skip is None else _DT[skip.dtype], _p(skip_coef), 1, _p(weight),
+                                  _p(bias), n, dm, float(eps), 1 if rms else 0, 1 if few_rows else 0,
+                                  _stream()), "norm_residual")
+    return x
+
+
+def short_conv(x: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], row_pos: torch.Tensor,
+               row_seq: torch.Tensor, seq_slot: torch.Tensor, out_dtype: torch.dtype,
+               write_h: bool = True, write_state: bool = True) -> Optional[torch.Tensor]:
+    """h = x + a causal convolution over time on every channel.  x: float32 [n, dm]; w: float32
+    [dm, taps]; state: float32 [slots, taps - 1, dm] (None with one tap), the last inputs of
+    every slot's sequence, read for positions before the step's rows and written for the
+    step's last ones.  Both in one call only where every sequence starts at position 0 or
+    brings one row."""
+    _need(x, "x", torch.float32, (None, None))
+    n, dm = x.shape
+    _need(w, "w", torch.float32, (dm, None))
+    taps = w.shape[1]
+    if taps > 1:
+        _need(state, "state", torch.float32, (None, taps - 1, dm))
+    out = torch.empty((n, dm), dtype=out_dtype, device=x.device) if write_h else None
+    what = (1 if write_h else 0) | (2 if write_state and taps > 1 else 0)
+    _check(lib().jb_short_conv(_p(x), _p(w), _p(state), (taps - 1) * dm, _p(row_pos), _p(row_seq),
+                               _p(seq_slot), _p(out), _DT[out_dtype], n, dm, taps, what, _stream()),
+           "short_conv")
+    return out
+
+
+def mingru(P: torch.Tensor, width: int, bias: Optional[torch.Tensor], state: torch.Tensor,
+           row_seq: torch.Tensor, seq_slot: torch.Tensor, out_dtype: torch.dtype,
+           every_row_starts: bool = False, col0: int = 0) -> torch.Tensor:
+    """The minGRU's recurrence over the rows from the sums P [S, n, ld] of [z | x | g] (from
+    column col0 on, ``width`` each; bias float32 [3 width] or None): S * silu(g) as
+    [n, width].  state: float32 [slots, width], read and left updated."""
+    P = stack(P)
+    _need(P, "P", torch.float32, (None, None, None))
+    S, n, ld = P.shape
+    _need(state, "state", torch.float32, (None, width))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (3 * width,))
+    n_seqs = seq_slot.numel()
+    L = lib()
+    need = int(L.jb_mingru_scratch(n, n_seqs, width, 1 if every_row_starts else 0))
+    scratch = _scratch(P.device, need) if need > 0 else None
+    out = torch.empty((n, width), dtype=out_dtype, device=P.device)
+    _check(L.jb_mingru(_p(P), S, n * ld, ld, col0, _p(bias), _p(state), _p(row_seq), _p(seq_slot),
+                       _p(scratch), _p(out), _DT[out_dtype], n, n_seqs, width,
+                       1 if every_row_starts else 0, _stream()), "mingru", 3 if need > 0 else 1)
+    return out
+
+
+def moe_route(P: torch.Tensor, col0: int, outputs: int, correction: Optional[torch.Tensor], groups: int,
+              keep: int, top: int, first_identity: int, scale: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The router of a routed feed-forward over the logits in columns col0 .. col0 + outputs - 1
+    of the sums P [S, n, ld]: (weights [n, outputs], 0 for outputs not chosen; the summed
+    weight of the chosen outputs from first_identity on, [n])."""
+    P = stack(P)
+    _need(P, "P", torch.float32, (None, None, None))
+    S, n, ld = P.shape
+    if correction is not None:
+        _need(correction, "correction", torch.float32, (outputs,))
+    weights = torch.empty((n, outputs), dtype=torch.float32, device=P.device)
+    skip = torch.empty((n,), dtype=torch.float32, device=P.device)
+    _check(lib().jb_moe_route(_p(P), S, n * ld, ld, col0, _p(correction), _p(weights), _p(skip), n, outputs,
+                              groups, keep, top, first_identity, float(scale), _stream()), "moe_route")
+    return weights, skip
+
+
+def activation_weighted(z: torch.Tensor, width: int, weights: torch.Tensor, n_experts: int, ff: int,
+                        kind: str, out_dtype: torch.dtype) -> torch.Tensor:
+    """act(sum z) * weights[row, column // ff] over the first n_experts * ff columns of z
+    [S, n, ld], act alone over the rest up to ``width``."""
+    z = stack(z)
+    _need(z, "z", torch.float32, (None, None, None))
+    S, n, ld = z.shape
+    _need(weights, "weights", torch.float32, (n, None))
+    out = torch.empty((n, width), dtype=out_dtype, device=z.device)
+    _check(lib().jb_activation_weighted(_p(z), S, n * ld, ld, _p(weights), weights.shape[1], n_experts, ff,
+                                        ACTIVATIONS[kind], _p(out), _DT[out_dtype], n, width, _stream()),
+           "activation_weighted")
+    return out
+
+
+def qkv_prepare_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_weight: Optional[torch.Tensor],
+                       k_weight: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
+                       sin: Optional[torch.Tensor], row_pos: torch.Tensor, row_seq: torch.Tensor,
+                       block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                       num_heads: int) -> torch.Tensor:
+    """q, k, v out of the sums of one product [S, n, ld] = [q | k | v | ...]: the bias, an RMS
+    norm per head on q and k (weights float32 [hd] or None), a rotation of the first
+    2 * cos.shape[1] values of each head (value i with value i + cos.shape[1]), K and V
+    into the cache pages at the rows' positions.  Returns q [n, heads, hd] in the cache's type."""
+    qkv = stack(qkv)
+    _need(qkv, "qkv", torch.float32, (None, None, None))
+    S, n, ld = qkv.shape
+    _need(k_cache, "k_cache", _FLOATS, (None, None, PAGE, None))
+    nkv, hd = k_cache.shape[1], k_cache.shape[3]
+    _need(v_cache, "v_cache", k_cache.dtype, (k_cache.shape[0], nkv, PAGE, None))
+    vd = v_cache.shape[3]
+    rot_half = 0 if cos is None else cos.shape[1]
+    if cos is not None:
+        _need(cos, "cos", torch.float32, (None, rot_half))
+        _need(sin, "sin", torch.float32, (cos.shape[0], rot_half))
+    q = torch.empty((n, num_heads, hd), dtype=k_cache.dtype, device=qkv.device)
+    _check(lib().jb_qkv_prepare_append(_p(qkv), S, n * ld, ld, _p(bias), _p(q_weight), _p(k_weight),
+                                       float(eps), _p(cos), _p(sin), rot_half, _p(row_pos), _p(row_seq),
+                                       _p(block_table), block_table.shape[1], _p(q), _p(k_cache),
+                                       _p(v_cache), _DT[k_cache.dtype], n, num_heads, nkv, hd, vd,
+                                       _stream()), "qkv_prepare_append")
+    return q
+
+
 def latent_down(P: torch.Tensor, q_rank: int, wq: Optional[torch.Tensor], kv_rank: int,
                 wkv: torch.Tensor, rot_dim: int, cos: Optional[torch.Tensor],
                 sin: Optional[torch.Tensor], row_pos: torch.Tensor, row_seq: torch.Tensor,
@@ -549,8 +682,14 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               head_scale: Optional[torch.Tensor] = None,
               sink: Optional[torch.Tensor] = None, softcap: float = 0.0,
               slopes: Optional[torch.Tensor] = None, value_dim: int = 0,
-              head_major: bool = False) -> torch.Tensor:
+              head_major: bool = False, keep_first: int = 0,
+              score_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal GQA attention of every row over its sequence's cache pages.
+
+    ``keep_first`` > 0 (with a window): positions below it stay visible to every later
+    row beside the window; ``max_chunks`` then counts their chunks too
+    (``attention_kept_chunks``).  ``score_bias`` (float32 [heads]): the weight of a visible
+    key is sigmoid(score + score_bias[head]), not normalized over the keys (no softmax).
 
     ``softcap`` > 0: a score s becomes softcap * tanh(s / softcap); ``slopes`` (float32
     [heads]): slopes[h] * (the row's position - the key's) is taken off the score, after
@@ -596,8 +735,10 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     _need(block_table, "block_table", torch.int32, (None, None))
     out = torch.empty((nh, n, vd) if head_major else (n, nh, vd), dtype=q.dtype, device=q.device)
     L = lib()
+    if score_bias is not None:
+        _need(score_bias, "score_bias", torch.float32, (nh,))
     tc = (not force_simt and vd == hd and q.dtype == torch.bfloat16
-          and v_ld == 0 and not head_major
+          and v_ld == 0 and not head_major and not keep_first and score_bias is None
           and (decode or blocks is not None) and bool(L.jb_attn_tc_ok(nh, nkv, hd))
           and (decode or head_scale is None or bool((head_scale > 0).all())))
     if tc and not decode:
@@ -637,12 +778,12 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                                              cnt, nh, hd, window, parts, per_cta, _p(sink),
                                              _stream()), "attention merge")
         else:
-            _check(L.jb_attention_ext(_p(q), _p(k_cache), _p(v_cache), _DT[q.dtype], _p(row_pos),
+            _check(L.jb_attention_gen(_p(q), _p(k_cache), _p(v_cache), _DT[q.dtype], _p(row_pos),
                                       _p(row_seq), _p(block_table), block_table.shape[1],
                                       _p(scratch), _p(out), row0, cnt, nh, nkv, hd, vd, window,
                                       float(scale), _p(head_scale), _p(sink), max_chunks, v_ld,
                                       float(softcap), _p(slopes), n if head_major else 0,
-                                      _stream()), "attention", kernels=2)
+                                      int(keep_first), _p(score_bias), _stream()), "attention", kernels=2)
     return out
 
 
