@@ -140,16 +140,22 @@ def mingru_candidate(u: torch.Tensor) -> torch.Tensor:
     return torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
 
 
-def mingru_mixer(h, w, pre, m, rounding=None, state=None):
-    T = h.shape[0]
-    z = torch.sigmoid(h @ w[pre + "z"].T + w[pre + "z.b"])
-    c = mingru_candidate(h @ w[pre + "x"].T + w[pre + "x.b"])
-    g = h @ w[pre + "g"].T
-    S = torch.zeros(m["width"]) if state is None else state.clone()
-    out = torch.zeros(T, m["width"])
+def mingru_recurrence(zl, u, g, state=None):
+    """zl, u, g [T, W]: the gate's and the candidate's pre-activations and the output gate's;
+    -> (S_t * silu(g_t) [T, W], the last state)."""
+    T, W = zl.shape
+    z, c = torch.sigmoid(zl), mingru_candidate(u)
+    S = torch.zeros(W) if state is None else state.clone()
+    out = torch.zeros(T, W)
     for t in range(T):
         S = (1 - z[t]) * S + z[t] * c[t]
         out[t] = S * (g[t] * torch.sigmoid(g[t]))
+    return out, S
+
+
+def mingru_mixer(h, w, pre, m, rounding=None, state=None):
+    out, S = mingru_recurrence(h @ w[pre + "z"].T + w[pre + "z.b"], h @ w[pre + "x"].T + w[pre + "x.b"],
+                               h @ w[pre + "g"].T, state)
     out = _round(out, rounding)
     return out @ w[pre + "o"].T, S
 
