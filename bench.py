@@ -9,6 +9,7 @@
     python bench.py --only generate [--model 8b] ...      (unequal prompts, then 256 tokens each)
     python bench.py --only zuzelorn [--layers 8]           (the Zuzelorn design beside Qwen3 at equal sizes)
     python bench.py --only dunavik [--design-size 4b]      (the Dunavik design beside Zuzelorn at equal sizes)
+    python bench.py --only kefesun [--design-size 4b]      (the Kefesun design beside Dunavik's attention layers)
 
 The default run has the layer sizes of Qwen3-4B (36 layers, hidden 2560, 32
 heads, 8 KV heads, head size 128, feed-forward 9728, vocabulary 151936, tied
@@ -446,6 +447,55 @@ def dunavik_flops(cfg, tokens, window):
     return total + 2 * dm * cfg["vocab"]
 
 
+def kefesun_cfg(size, n_layers, vocab, mixers="mixed", window=1024):
+    """A Kefesun config.json of the given layer sizes.  mixers: "attention" (every layer the
+    sigmoid attention with a window and kept first tokens), "mingru" (every layer the minGRU) or
+    "mixed" (every third layer a minGRU, the second one first).  The routed feed-forward holds as
+    many weights as the dense one of the size: six experts of an eighth of its width each, two
+    identity experts, a shared expert of a quarter; two of the eight per token, from two of four
+    groups."""
+    dm, nh, nkv, hd, ff = DESIGN_SIZES[size]
+    mlp = {"expert": {"ff": ff // 8}, "kind": "moe",
+           "router": {"experts": 6, "groups": {"count": 4, "keep": 2}, "identity": 2, "scale": 1.5, "top": 2},
+           "shared": {"ff": ff // 4}}
+    layers = []
+    for i in range(n_layers):
+        if mixers == "mingru" or (mixers == "mixed" and i % 3 == 1):
+            layers.append({"type": "mingru", "mixer": {"width": dm}, "mlp": mlp})
+        else:
+            m = {"dim": hd, "heads": nh, "kv_heads": nkv, "mask": {"keep_first": 4, "size": window},
+                 "rot": {"base": 10000.0, "dims": hd // 2}, "scale": hd ** -0.5, "vdim": hd}
+            layers.append({"type": "attention", "mixer": m, "mlp": mlp})
+    return {"architecture": "Kefesun", "canon": {"taps": 4}, "embedding": {"scale": 1.0}, "layers": layers,
+            "norm": {"eps": 1e-5}, "vocab": vocab, "width": dm}
+
+
+def kefesun_flops(cfg, tokens):
+    """Multiply-adds times two of one prompt of a Kefesun model: (what the design asks for: the
+    products of the experts a token chose, all of them counted as experts with matrices; what
+    the engine runs: every expert's products for every token).  Both with the mixers' products,
+    the attention over the keys a row sees and the head for one row."""
+    dm, asked, run = cfg["width"], 0.0, 0.0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "mingru":
+            mats, attn = 4 * dm * m["width"], 0.0
+        else:
+            H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            mats = dm * (H * D + G * D + G * Dv) + H * Dv * dm
+            w, keep = m.get("mask", {}).get("size", 0) or tokens, m.get("mask", {}).get("keep_first", 0)
+            pairs = sum(min(i + 1, w + min(keep, max(0, i + 1 - w))) for i in range(tokens))
+            attn = 2 * H * (D + Dv) * pairs
+        f = layer["mlp"]
+        r = f["router"]
+        shared = (f.get("shared") or {}).get("ff", 0)
+        outs = r["experts"] + r.get("identity", 0)
+        asked += 2 * (mats + dm * outs + 2 * dm * (r["top"] * f["expert"]["ff"] + shared)) * tokens + attn
+        run += 2 * (mats + dm * outs + 2 * dm * (r["experts"] * f["expert"]["ff"] + shared)) * tokens + attn
+    head = 2 * dm * cfg["vocab"]
+    return asked + head, run + head
+
+
 def qwen3_cfg(size, n_layers, vocab, max_positions):
     dm, nh, nkv, hd, ff = DESIGN_SIZES[size]
     return dict(QWEN3_4B, num_hidden_layers=n_layers, hidden_size=dm, num_attention_heads=nh,
@@ -518,13 +568,23 @@ def design_compare(args):
             designs = [("zuzelorn", zuzelorn_cfg(size, n_layers, vocab, max_positions))]
             designs += [(f"dunavik-{mx}", dunavik_cfg(size, n_layers, vocab, mx, args.window))
                         for mx in args.mixers.split(",")]
+        if args.only == "kefesun":
+            # beside Dunavik's attention layers: a window, layer norms, a feed-forward of two
+            # matrices around a squared relu, float32 residual
+            designs = [("dunavik-attention", dunavik_cfg(size, n_layers, vocab, "attention", args.window))]
+            designs += [(f"kefesun-{mx}", kefesun_cfg(size, n_layers, vocab, mx, args.window))
+                        for mx in args.mixers.replace("latent", "mingru").split(",")]
         for design, cfg in designs:
             rng = np.random.default_rng(0)
             eng = Engine.open_random(cfg, seed=0, dtype=args.dtype, max_tokens=max(room * batch, T + 64),
                                      max_seqs=batch, n_ctx=max_positions)
             pre_ms = prefill_timed(eng, rng, T)
-            flops = (dunavik_flops(cfg, T, args.window) if design.startswith("dunavik")
-                     else design_flops(design.split("-")[0], size, n_layers, T, vocab))
+            flops_run = None
+            if design.startswith("kefesun"):
+                flops, flops_run = kefesun_flops(cfg, T)
+            else:
+                flops = (dunavik_flops(cfg, T, args.window) if design.startswith("dunavik")
+                         else design_flops(design.split("-")[0], size, n_layers, T, vocab))
 
             def one_prefill():
                 s = eng.new_sequence()
@@ -554,6 +614,10 @@ def design_compare(args):
                     "decode_kernels_us_per_step": {k: [v[0] // 3, round(v[1] / 3, 2), round(v[2] / 3, 2)]
                                                    for k, v in sorted(dec_kernels.items(),
                                                                       key=lambda kv: -kv[1][1])}}
+            if flops_run is not None:
+                # the routed feed-forward runs every expert for every token: the products that
+                # were run beside the ones the design asks for
+                line["prefill"]["tflops_run"] = round(flops_run / pre_ms / 1e9, 1)
             print(json.dumps(line), flush=True)
             eng.close()
             del eng
@@ -596,7 +660,7 @@ def main():
     ap.add_argument("--share", type=int, default=0,
                     help="--only zuzelorn: also a model whose layers share keys and values in groups of this many")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "prefill-timeline", "generate",
-                                                    "zuzelorn", "dunavik"],
+                                                    "zuzelorn", "dunavik", "kefesun"],
                     help="run one part only and print its time (for profiling; no JSON line "
                          "but for generate); prefill-timeline: each kernel's share of one prefill "
                          "step; timeline: when each kernel of one replayed decode "
@@ -614,7 +678,7 @@ def main():
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
-    if args.only in ("zuzelorn", "dunavik"):
+    if args.only in ("zuzelorn", "dunavik", "kefesun"):
         args.warmup = max(args.warmup, 3)
         return design_compare(args)
     full_layers = MODELS[args.model]["num_hidden_layers"]

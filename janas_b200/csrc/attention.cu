@@ -913,18 +913,31 @@ extern "C" int jb_attention_merge_sink(const float *scratch, const int32_t *row_
                                        int max_parts, int chunks_per_part, const float *sink,
                                        cudaStream_t st)
 {
+    return jb_attention_merge_gen(scratch, row_pos, out, dt, row0, n_rows, nh, hd, window, max_parts,
+                                  chunks_per_part, sink, 0, 0, st);
+}
+
+// The same for a mixer with kept first tokens (their chunks are a row's first partials, one
+// chunk each, before the window's) and, with plain_sum, for weights that are not normalized
+// over the keys: the partials' weighted values are added and nothing is divided.
+extern "C" int jb_attention_merge_gen(const float *scratch, const int32_t *row_pos, void *out,
+                                      int dt, int row0, int n_rows, int nh, int hd, int window,
+                                      int max_parts, int chunks_per_part, const float *sink,
+                                      int keep_first, int plain_sum, cudaStream_t st)
+{
     if (n_rows <= 0)
         return JB_OK;
-    if (hd <= 0 || hd > 512 || nh <= 0 || nh > 65535 || max_parts <= 0 || chunks_per_part <= 0)
+    if (hd <= 0 || hd > 512 || nh <= 0 || nh > 65535 || max_parts <= 0 || chunks_per_part <= 0 ||
+        keep_first < 0 || (plain_sum && sink != nullptr))
         return JB_EINVAL;
     dim3 grid(n_rows, nh);
     int threads = (hd + 31) / 32 * 32;
     if (dt == JB_F32)
         launch(attn_merge_kernel<float>, grid, threads, 0, st, scratch, row_pos, (float *)out, row0,
-               nh, hd, window, max_parts, chunks_per_part, sink, 0ll, 0, 0);
+               nh, hd, window, max_parts, chunks_per_part, sink, 0ll, keep_first, plain_sum);
     else if (dt == JB_BF16)
         launch(attn_merge_kernel<bf16>, grid, threads, 0, st, scratch, row_pos, (bf16 *)out, row0,
-               nh, hd, window, max_parts, chunks_per_part, sink, 0ll, 0, 0);
+               nh, hd, window, max_parts, chunks_per_part, sink, 0ll, keep_first, plain_sum);
     else
         return JB_EINVAL;
     return launch_status();

@@ -403,7 +403,11 @@ template <int HD> struct PrefillCfg {
     static constexpr int TMEM_COLS = 512;
 };
 
-template <int HD, bool EXT>
+// MODE 0: softmax; 1: softmax of scores with a cap or slopes (ScoreExt); 2: weights that are
+// sigmoid(score + score_bias[head]), not normalized over the keys.  keep_first > 0 (with a
+// window): the first keep_first positions stay visible beside the window; their chunks, as
+// far as they lie before the run's first chunk, come first in the CTA's order of chunks.
+template <int HD, int MODE>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_k,
@@ -411,10 +415,12 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                        const int32_t *__restrict__ block_table, int bt_stride,
                        bf16 *__restrict__ out, int nh, int nkv, int G, int R, int window,
                        float scale, const float *__restrict__ head_scale,
-                       const float *__restrict__ sink, const ScoreExt x)
+                       const float *__restrict__ sink, const ScoreExt x, int keep_first,
+                       const float *__restrict__ score_bias)
 {
     using Cfg = PrefillCfg<HD>;
     constexpr int NB = Cfg::NB;
+    constexpr bool EXT = MODE == 1, SIG = MODE == 2;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *q_s = smem;                           // two tiles
     uint8_t *p_s = q_s + 2 * Cfg::Q_TILE;          // two tiles
@@ -440,9 +446,12 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     int lo0 = window > 0 && q_pos + 1 > window ? q_pos + 1 - window : 0;
     int c_first = lo0 / AT_KEYS;
     int c_last = (q_pos + q_count - 1) / AT_KEYS;
-    int n_chunks = c_last - c_first + 1;
+    // the kept first tokens' chunks that lie wholly before every row's window
+    int n_keep = window > 0 && keep_first > 0 ? min(c_first, (keep_first + AT_KEYS - 1) / AT_KEYS) : 0;
+    int n_chunks = n_keep + c_last - c_first + 1;
     if (n_chunks <= 0)
         return;
+    auto chunk_at = [&](int i) { return i < n_keep ? i : c_first + i - n_keep; };
 
     uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8 * i; };
@@ -496,7 +505,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
             int chunk = u == 0 ? 0 : u == 2 * n_chunks - 1 ? n_chunks - 1 : is_v ? (u - 2) / 2
                                                                             : (u + 1) / 2;
             const CUtensorMap *map = is_v ? &map_v : &map_k;
-            int c = c_first + chunk;
+            int c = chunk_at(chunk);
 #pragma unroll
             for (int pg = 0; pg < 2; pg++) {
                 int idx = 2 * c + pg;
@@ -617,10 +626,12 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         const float inv_cap2 = EXT && x.cap2 > 0.0f ? 1.0f / x.cap2 : 0.0f;
         const float slope2 = EXT && x.slopes != nullptr && live
                                  ? x.slopes[kvh * G + g] * 1.4426950408889634f : 0.0f;
+        // a head's number added to its scores before the sigmoid, in log2 units
+        const float sb2 = SIG && live ? score_bias[kvh * G + g] * 1.4426950408889634f : 0.0f;
         float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
         for (int it = 0; it < n_chunks && tile_live; it++) {
-            int t0 = (c_first + it) * AT_KEYS;              // the chunk's first key
+            int t0 = chunk_at(it) * AT_KEYS;                // the chunk's first key
             ok = ok && mbar_wait(bar(7 + t), it & 1, abort, err, 27);
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
@@ -637,9 +648,33 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                 // most chunks lie wholly inside every row's range: no key is masked.
                 // The maximum is taken over the raw scores (the scale is positive)
                 // and scaled once; the scale itself goes into the exponent's FMA.
-                bool inside = t0 + AT_KEYS - 1 <= pos_first && t0 >= lo_last;
+                bool inside = t0 + AT_KEYS - 1 <= pos_first &&
+                              (t0 >= lo_last || t0 + AT_KEYS <= keep_first);
                 float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                if constexpr (EXT) {
+                if constexpr (SIG) {
+                    // every visible key's weight by itself: no maximum, no sum; two
+                    // bfloat16 to a register, in place of the scores
+                    if (inside && live) {
+#pragma unroll
+                        for (int i = 0; i < AT_KEYS / 2; i++) {
+                            float p0 = fast_sigmoid2(fmaf(__uint_as_float(raw[2 * i]), c2, sb2));
+                            float p1 = fast_sigmoid2(fmaf(__uint_as_float(raw[2 * i + 1]), c2, sb2));
+                            __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                            raw[i] = *reinterpret_cast<uint32_t *>(&pk);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < AT_KEYS / 2; i++) {
+                            int key = t0 + 2 * i;
+                            bool s0 = live && key <= pos && (key >= lo || key < keep_first);
+                            bool s1 = live && key + 1 <= pos && (key + 1 >= lo || key + 1 < keep_first);
+                            float p0 = s0 ? fast_sigmoid2(fmaf(__uint_as_float(raw[2 * i]), c2, sb2)) : 0.0f;
+                            float p1 = s1 ? fast_sigmoid2(fmaf(__uint_as_float(raw[2 * i + 1]), c2, sb2)) : 0.0f;
+                            __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                            raw[i] = *reinterpret_cast<uint32_t *>(&pk);
+                        }
+                    }
+                } else if constexpr (EXT) {
                     // every score goes through the cap and loses its head's slope times the
                     // key's distance back: in log2 units, in place of the raw score.  Key
                     // t0 + i is pos - t0 - i back: the slope's term is slope2 * i + sbase.
@@ -666,7 +701,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                                 float r = __uint_as_float(raw[i + e]);
                                 float bias = fmaf(slope2, (float)(i + e), sbase);
                                 float v = capped ? fmaf(x.cap2, fast_tanh(r * k1), bias) : fmaf(r, c2, bias);
-                                v = (live && key <= pos && key >= lo) ? v : -INFINITY;
+                                v = (live && key <= pos && (key >= lo || key < keep_first)) ? v : -INFINITY;
                                 raw[i + e] = __float_as_uint(v);
                                 m4[e] = fmaxf(m4[e], v);
                             }
@@ -683,7 +718,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
                             int key = t0 + i + e;
-                            float v = (live && key <= pos && key >= lo)
+                            float v = (live && key <= pos && (key >= lo || key < keep_first))
                                           ? __uint_as_float(raw[i + e]) : -INFINITY;
                             raw[i + e] = __float_as_uint(v);
                             m4[e] = fmaxf(m4[e], v);
@@ -692,7 +727,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                 mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * c2x;
             }
             // move the row's reference only when the maximum has run far ahead of it
-            bool move = mx > m_ref + PF_LAZY || (m_ref == -INFINITY && mx > -INFINITY);
+            bool move = !SIG && (mx > m_ref + PF_LAZY || (m_ref == -INFINITY && mx > -INFINITY));
             float alpha = 1.0f;
             if (move) {
                 alpha = m_ref == -INFINITY ? 0.0f : exp2f(m_ref - mx);
@@ -705,7 +740,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
             // the weights, two bfloat16 to a register, in place of the scores
             float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int i = 0; i < AT_KEYS / 2; i += 4) {
+            for (int i = 0; i < (SIG ? 0 : AT_KEYS / 2); i += 4) {
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     float p0 = fast_exp2(fmaf(__uint_as_float(raw[2 * (i + e)]), c2x, -m_use));
@@ -753,8 +788,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
             ok = ok && mbar_wait(bar(11 + t), (n_chunks - 1) & 1, abort, err, 29);
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
-            float inv = 1.0f / l_run;
-            if (sink != nullptr && live) {
+            float inv = SIG ? 1.0f : 1.0f / l_run;
+            if (!SIG && sink != nullptr && live) {
                 // the head's sink joins the denominator: 2^(sink - m) beside l, with the
                 // larger of the two as the reference so that neither overflows
                 float s2 = sink[kvh * G + g] * 1.4426950408889634f;
@@ -837,6 +872,10 @@ struct DecodeQkv {
     long long ld;                // floats from one row of qkv to the next; 0: (nh + 2 nkv) HD
     float cap2;                  // ScoreExt's fields: a cap on the scores (0: none) ...
     const float *slopes;         // ... and a slope per head on the distance back, or nullptr
+    int keep_first;              // with a window: the first positions that stay visible beside it
+                                 // (without qkv only); their chunks are the first partials of a row
+    const float *score_bias;     // per head, or nullptr: weights are sigmoid(score + this), not
+                                 // normalized over the keys (no cap, slopes or head factors then)
 };
 
 __device__ __forceinline__ float4 load_w4(const void *w, int w_f32, int at)
@@ -876,7 +915,10 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         prefetch_tensor_map(&map_q);
     }
     int kvh = blockIdx.y;
-    int parts = (max_chunks + chunks_per_cta - 1) / chunks_per_cta;
+    // max_chunks counts the kept first tokens' chunks (kc, one partial each, first among a
+    // row's partials) and then the window's, chunks_per_cta to a partial
+    int kc = window > 0 && f.keep_first > 0 ? (f.keep_first + AT_KEYS - 1) / AT_KEYS : 0;
+    int parts = kc + (max_chunks - kc + chunks_per_cta - 1) / chunks_per_cta;
     int max_parts = parts;             // partials per (row, head) in scratch
     int lrow = blockIdx.x / parts, part_i = blockIdx.x % parts;
     int q_row = row0 + lrow;
@@ -884,17 +926,21 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
     int seq = row_seq[q_row];
     int lo = window > 0 && q_pos + 1 > window ? q_pos + 1 - window : 0;
     int c_base = lo / AT_KEYS;
-    int c_first = c_base + part_i * chunks_per_cta;
-    int c_last = min(q_pos / AT_KEYS, c_first + chunks_per_cta - 1);
+    const bool kept_part = part_i < kc;
+    int c_first = kept_part ? part_i : c_base + (part_i - kc) * chunks_per_cta;
+    int c_last = kept_part ? part_i : min(q_pos / AT_KEYS, c_first + chunks_per_cta - 1);
     int n_chunks = c_last - c_first + 1;
     if (n_chunks <= 0)
         return;
+    // a kept chunk shows its keys before the window and before keep_first (a chunk with no
+    // such key leaves an empty partial); the window's chunks show the window's keys
+    const int kept_end = min(f.keep_first, lo);
 
     uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8 * i; };
     const bool fused = f.qkv != nullptr;
     // this CTA's run holds the chunk of the new position: it appends the key and value
-    const bool appends = fused && f.k_cache != nullptr && c_last == q_pos / AT_KEYS;
+    const bool appends = fused && f.k_cache != nullptr && !kept_part && c_last == q_pos / AT_KEYS;
     if (threadIdx.x == 0) {
         mbar_init(bar(0), fused ? AT_ROWS : 1);
         for (int s = 0; s < DQ_UNITS; s++) {
@@ -1159,6 +1205,11 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
         for (int g = 0; g < GP; g++)
             slope2[g] = f.slopes != nullptr && g < G ? f.slopes[kvh * G + g] * 1.4426950408889634f : 0.0f;
+        const bool sig = f.score_bias != nullptr;
+        float sb2[GP];
+#pragma unroll
+        for (int g = 0; g < GP; g++)
+            sb2[g] = sig && g < G ? f.score_bias[kvh * G + g] * 1.4426950408889634f : 0.0f;
         bool ok = true;
         // running over this CTA's chunks: maximum, sum (every thread keeps all heads')
         // and this thread's value of O for every head
@@ -1188,7 +1239,7 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int it = 0; it < n_chunks; it++) {
             int c = c_first + it;
             int t = c * AT_KEYS + r;
-            bool visible = t <= q_pos && t >= lo;
+            bool visible = kept_part ? t < kept_end : t <= q_pos && t >= lo;
             ok = ok && mbar_wait(bar(7 + (it & 1)), (it >> 1) & 1, abort, err, 17);
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
@@ -1200,8 +1251,14 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
                 float v = (ok && visible && g < G) ? sc[g] * c2[g] : -INFINITY;
                 if (ext && v != -INFINITY)
                     v = ext_score(v, f.cap2, inv_cap2, slope2[g], q_pos - t);
-                sc[g] = v;
-                m[g] = warp_max(v);
+                if (sig) {
+                    // the weight by itself; the reference stays 0 and the partials are sums
+                    sc[g] = v == -INFINITY ? 0.0f : fast_sigmoid2(v + sb2[g]);
+                    m[g] = 0.0f;
+                } else {
+                    sc[g] = v;
+                    m[g] = warp_max(v);
+                }
             }
             if (lane == 0) {
 #pragma unroll
@@ -1222,7 +1279,7 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
                 if (mn == -INFINITY)
                     alpha[g] = 1.0f;
                 m_run[g] = mn;
-                float p = sc[g] == -INFINITY ? 0.0f : exp2f(sc[g] - mn);
+                float p = sig ? sc[g] : sc[g] == -INFINITY ? 0.0f : exp2f(sc[g] - mn);
                 sc[g] = p;
                 l[g] = warp_sum(p);
             }
@@ -1408,8 +1465,29 @@ extern "C" int jb_attn_tc_prefill_ext(const void *q, const void *k_cache, const 
                                       const float *head_scale, const float *sink, float softcap,
                                       const float *slopes, cudaStream_t st)
 {
-    if (!jb_attn_tc_ok(nh, nkv, hd) || n <= 0 || softcap < 0.0f)
+    return jb_attn_tc_prefill_gen(q, k_cache, v_cache, n_pages, qblk, n_blocks, block_table, bt_stride,
+                                  out, n, nh, nkv, hd, window, scale, head_scale, sink, softcap, slopes,
+                                  0, nullptr, st);
+}
+
+// The same with two more things.  keep_first > 0 (with a window): the first keep_first
+// positions of a sequence stay visible beside the window, at their true positions.
+// score_bias (float [nh], or null): a key's weight is sigmoid(score + score_bias[head]), not
+// normalized over the keys; it goes with no sink, head factor, cap or slopes.
+extern "C" int jb_attn_tc_prefill_gen(const void *q, const void *k_cache, const void *v_cache,
+                                      long long n_pages, const int32_t *qblk, int n_blocks,
+                                      const int32_t *block_table, int bt_stride, void *out, int n,
+                                      int nh, int nkv, int hd, int window, float scale,
+                                      const float *head_scale, const float *sink, float softcap,
+                                      const float *slopes, int keep_first, const float *score_bias,
+                                      cudaStream_t st)
+{
+    if (!jb_attn_tc_ok(nh, nkv, hd) || n <= 0 || softcap < 0.0f || keep_first < 0)
         return JB_EINVAL;
+    if (score_bias != nullptr && (sink != nullptr || head_scale != nullptr || softcap > 0.0f || slopes != nullptr))
+        return JB_EINVAL;
+    if (window <= 0)
+        keep_first = 0;
     ScoreExt x = score_ext(softcap, slopes);
     int G = nh / nkv;
     int R = AT_ROWS / G;               // positions of one block; qblk's runs hold up to 2 R
@@ -1420,24 +1498,29 @@ extern "C" int jb_attn_tc_prefill_ext(const void *q, const void *k_cache, const 
         return JB_EINVAL;
     if (n_blocks <= 0)
         return JB_OK;
-#define JB_PF(HDV, EXT)                                                                        \
+#define JB_PF(HDV, MODE)                                                                       \
     do {                                                                                       \
         static unsigned long long smem_allowed = 0;                                            \
-        auto kern = attn_tc_prefill_kernel<HDV, EXT>;                                          \
+        auto kern = attn_tc_prefill_kernel<HDV, MODE>;                                         \
         if (!allow_dynamic_smem(kern, PrefillCfg<HDV>::SMEM_BYTES, smem_allowed))              \
             return JB_ELAUNCH;                                                                 \
         launch(kern, dim3((unsigned)n_blocks * nkv), PF_THREADS,                               \
                PrefillCfg<HDV>::SMEM_BYTES, st, mq, mk, mv, qblk, block_table, bt_stride,      \
-               (bf16 *)out, nh, nkv, G, R, window, scale, head_scale, sink, x);                \
+               (bf16 *)out, nh, nkv, G, R, window, scale, head_scale, sink, x, keep_first,     \
+               score_bias);                                                                    \
     } while (0)
-    if (hd == 128 && x.on())
-        JB_PF(128, true);
+    if (hd == 128 && score_bias != nullptr)
+        JB_PF(128, 2);
+    else if (hd == 128 && x.on())
+        JB_PF(128, 1);
     else if (hd == 128)
-        JB_PF(128, false);
+        JB_PF(128, 0);
+    else if (score_bias != nullptr)
+        JB_PF(64, 2);
     else if (x.on())
-        JB_PF(64, true);
+        JB_PF(64, 1);
     else
-        JB_PF(64, false);
+        JB_PF(64, 0);
 #undef JB_PF
     return launch_status();
 }
@@ -1465,7 +1548,10 @@ static int attn_tc_decode(const void *q, const void *k_cache, const void *v_cach
             mq = mk;            // not used: the kernel makes q itself
         else if (!attn_tensor_map(q, hd, nh, n, G, 1, &mq))
             return JB_EINVAL;
-        unsigned gx = (unsigned)n_rows * ((max_chunks + chunks_per_cta - 1) / chunks_per_cta);
+        int kc = window > 0 && f.keep_first > 0 ? (f.keep_first + AT_KEYS - 1) / AT_KEYS : 0;
+        if (max_chunks <= kc || (kc > 0 && f.qkv != nullptr))
+            return JB_EINVAL;
+        unsigned gx = (unsigned)n_rows * (kc + (max_chunks - kc + chunks_per_cta - 1) / chunks_per_cta);
 #define JB_DQ(GP)                                                                              \
     do {                                                                                       \
         static unsigned long long smem_allowed = 0;                                            \
@@ -1488,6 +1574,8 @@ static int attn_tc_decode(const void *q, const void *k_cache, const void *v_cach
 #undef JB_DQ
         return launch_status();
     }
+    if (f.keep_first > 0 || f.score_bias != nullptr)
+        return JB_EINVAL;              // the kernel for the other sizes has neither
     if (hd == 128)
         return launch_attn_rows<128>(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table,
                                      bt_stride, part, n, nh, nkv, window, scale, max_chunks,
@@ -1543,6 +1631,34 @@ extern "C" int jb_attn_tc_decode_ext(const void *q, const void *k_cache, const v
     ScoreExt x = score_ext(softcap, slopes);
     f.cap2 = x.cap2;
     f.slopes = x.slopes;
+    return attn_tc_decode(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table, bt_stride,
+                          part, n, row0, n_rows, nh, nkv, hd, window, scale, max_chunks,
+                          chunks_per_cta, f, st);
+}
+
+// The same with kept first tokens and weights that are sigmoids (see jb_attn_tc_prefill_gen),
+// for the sizes of jb_attn_tc_decode_runs.  max_chunks counts the kept tokens' chunks
+// (jb_attention_kept_chunks), which are a row's first partials, one chunk each; the window's
+// follow, chunks_per_cta chunks to a partial.
+extern "C" int jb_attn_tc_decode_gen(const void *q, const void *k_cache, const void *v_cache,
+                                     long long n_pages, const int32_t *row_pos,
+                                     const int32_t *row_seq, const int32_t *block_table,
+                                     int bt_stride, float *part, int n, int row0, int n_rows,
+                                     int nh, int nkv, int hd, int window, float scale,
+                                     const float *head_scale, float softcap, const float *slopes,
+                                     int keep_first, const float *score_bias, int max_chunks,
+                                     int chunks_per_cta, cudaStream_t st)
+{
+    if (softcap < 0.0f || keep_first < 0 ||
+        (score_bias != nullptr && (head_scale != nullptr || softcap > 0.0f || slopes != nullptr)))
+        return JB_EINVAL;
+    DecodeQkv f = {};
+    f.head_scale = head_scale;
+    ScoreExt x = score_ext(softcap, slopes);
+    f.cap2 = x.cap2;
+    f.slopes = x.slopes;
+    f.keep_first = window > 0 ? keep_first : 0;
+    f.score_bias = score_bias;
     return attn_tc_decode(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table, bt_stride,
                           part, n, row0, n_rows, nh, nkv, hd, window, scale, max_chunks,
                           chunks_per_cta, f, st);

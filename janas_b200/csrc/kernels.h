@@ -207,6 +207,23 @@ int jb_attn_tc_decode_ext(const void *q, const void *k_cache, const void *v_cach
                           int n_rows, int nh, int nkv, int hd, int window, float scale,
                           const float *head_scale, float softcap, const float *slopes,
                           int max_chunks, int chunks_per_cta, cudaStream_t st);
+int jb_attn_tc_prefill_gen(const void *q, const void *k_cache, const void *v_cache,
+                           long long n_pages, const int32_t *qblk, int n_blocks,
+                           const int32_t *block_table, int bt_stride, void *out, int n, int nh,
+                           int nkv, int hd, int window, float scale, const float *head_scale,
+                           const float *sink, float softcap, const float *slopes, int keep_first,
+                           const float *score_bias, cudaStream_t st);
+int jb_attn_tc_decode_gen(const void *q, const void *k_cache, const void *v_cache,
+                          long long n_pages, const int32_t *row_pos, const int32_t *row_seq,
+                          const int32_t *block_table, int bt_stride, float *part, int n, int row0,
+                          int n_rows, int nh, int nkv, int hd, int window, float scale,
+                          const float *head_scale, float softcap, const float *slopes,
+                          int keep_first, const float *score_bias, int max_chunks,
+                          int chunks_per_cta, cudaStream_t st);
+int jb_attention_merge_gen(const float *scratch, const int32_t *row_pos, void *out, int dt,
+                           int row0, int n_rows, int nh, int hd, int window, int max_parts,
+                           int chunks_per_part, const float *sink, int keep_first, int plain_sum,
+                           cudaStream_t st);
 int jb_attn_tc_error(void);
 long long jb_gemm_simt_scratch(int n, int m, int k);
 int jb_gemm_simt(const void *A, int a_dt, const void *W, int w_dt, float *out, int n, int m, int k,

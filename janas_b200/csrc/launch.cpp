@@ -546,21 +546,32 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
     int vd = g.value_dim();
     Buf out = d.pool.get((size_t)n * (size_t)g.nh * (size_t)vd * dtype_size(c.dt));
     bool tc = !force_simt && vd == g.hd && c.dt == BF16 && (decode || blocks != nullptr) &&
-              !c.v_ld && !head_major && !g.keep_first && !g.score_bias &&
-              attention_tc_ok(g.nh, g.nkv, g.hd) && (decode || !g.head_scale || g.head_scale_positive);
+              !c.v_ld && !head_major && attention_tc_ok(g.nh, g.nkv, g.hd) &&
+              (decode || !g.head_scale || g.head_scale_positive);
+    // kept first tokens and weights that are sigmoids: the prefill kernel has them for all its
+    // sizes, of the decode kernels the one that runs over several chunks
+    bool special = g.keep_first || g.score_bias;
+    if (tc && special && ((decode && !jb_attn_tc_decode_runs(g.nh, g.nkv, g.hd)) ||
+                          (g.score_bias && (g.head_scale || g.sink || g.softcap != 0.0f || g.slopes))))
+        tc = false;
     if (tc && !decode) {
-        check(jb_attn_tc_prefill_ext(q, c.k, c.v, c.n_pages, blocks, n_blocks, c.block_table, c.bt_stride,
+        check(jb_attn_tc_prefill_gen(q, c.k, c.v, c.n_pages, blocks, n_blocks, c.block_table, c.bt_stride,
                                      out.ptr, ni, g.nh, g.nkv, g.hd, g.window, g.scale, g.head_scale,
-                                     g.sink, g.softcap, g.slopes, d.stream), "attention (tcgen05, prefill)");
+                                     g.sink, g.softcap, g.slopes, g.keep_first, g.score_bias, d.stream),
+              "attention (tcgen05, prefill)");
         return out;
     }
     int parts = max_chunks, per_cta = 1;
+    int kc = attention_kept_chunks(g.window, g.keep_first);
     if (tc) {
-        // CTAs per (token, KV head): each runs over per_cta chunks and leaves one partial
+        // CTAs per (token, KV head): each runs over per_cta chunks and leaves one partial;
+        // the kept first tokens' chunks are a CTA and a partial each, before the others
+        int win = std::max(max_chunks - kc, 1);
+        parts = win;
         if (jb_attn_tc_decode_runs(g.nh, g.nkv, g.hd))
-            parts = decode_parts(std::min<long long>(n, 4096) * g.nkv, max_chunks, 2 * d.sm_count);
-        per_cta = (max_chunks + parts - 1) / parts;
-        parts = (max_chunks + per_cta - 1) / per_cta;
+            parts = decode_parts(std::min<long long>(n, 4096) * g.nkv, win, 2 * d.sm_count);
+        per_cta = (win + parts - 1) / parts;
+        parts = kc + (win + per_cta - 1) / per_cta;
     }
     long long per_row = jb_attention_scratch(1, g.nh, vd, parts);
     long long rows_per_call = std::max<long long>(1, std::min<long long>(n, (long long)(ATT_SCRATCH_BYTES / 4) /
@@ -569,12 +580,14 @@ Buf attention(Device &d, const void *q, long long n, const AttnCache &c, const A
     for (long long row0 = 0; row0 < n; row0 += rows_per_call) {
         int cnt = (int)std::min<long long>(rows_per_call, n - row0);
         if (tc) {
-            check(jb_attn_tc_decode_ext(q, c.k, c.v, c.n_pages, row_pos, row_seq, c.block_table,
+            check(jb_attn_tc_decode_gen(q, c.k, c.v, c.n_pages, row_pos, row_seq, c.block_table,
                                         c.bt_stride, scratch.as<float>(), ni, (int)row0, cnt, g.nh, g.nkv,
                                         g.hd, g.window, g.scale, g.head_scale, g.softcap, g.slopes,
-                                        max_chunks, per_cta, d.stream), "attention (tcgen05, decode)");
-            check(jb_attention_merge_sink(scratch.as<float>(), row_pos, out.ptr, c.dt, (int)row0, cnt, g.nh,
-                                          g.hd, g.window, parts, per_cta, g.sink, d.stream), "attention merge");
+                                        g.keep_first, g.score_bias, std::max(max_chunks, kc + 1), per_cta,
+                                        d.stream), "attention (tcgen05, decode)");
+            check(jb_attention_merge_gen(scratch.as<float>(), row_pos, out.ptr, c.dt, (int)row0, cnt, g.nh,
+                                         g.hd, g.window, parts, per_cta, g.sink, g.keep_first,
+                                         g.score_bias ? 1 : 0, d.stream), "attention merge");
         } else {
             check(jb_attention_gen(q, c.k, c.v, c.dt, row_pos, row_seq, c.block_table, c.bt_stride,
                                    scratch.as<float>(), out.ptr, (int)row0, cnt, g.nh, g.nkv, g.hd, vd,

@@ -237,6 +237,8 @@ extern "C" int jb_activation_weighted(const float *z, int S, long long stride, i
 {
     if (n <= 0)
         return JB_OK;
+    if (n_experts == 0)
+        ff = 4;          // no weighted columns: the blocks' size only has to divide a thread's values
     if (width <= 0 || ld < width || ff <= 0 || n_experts < 0 || (long long)n_experts * ff > width ||
         (n_experts > 0 && (weights == nullptr || w_ld < n_experts)) || S <= 0 ||
         (kind != JB_ACT_RELU2 && kind != JB_ACT_RELU && kind != JB_ACT_GELU_TANH))

@@ -738,27 +738,38 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     if score_bias is not None:
         _need(score_bias, "score_bias", torch.float32, (nh,))
     tc = (not force_simt and vd == hd and q.dtype == torch.bfloat16
-          and v_ld == 0 and not head_major and not keep_first and score_bias is None
+          and v_ld == 0 and not head_major
           and (decode or blocks is not None) and bool(L.jb_attn_tc_ok(nh, nkv, hd))
           and (decode or head_scale is None or bool((head_scale > 0).all())))
+    # kept first tokens and sigmoid weights: the prefill kernel has them for all its sizes, of
+    # the decode kernels the one that runs over several chunks
+    if tc and (keep_first or score_bias is not None):
+        if decode and not L.jb_attn_tc_decode_runs(nh, nkv, hd):
+            tc = False
+        if score_bias is not None and (head_scale is not None or sink is not None or softcap
+                                       or slopes is not None):
+            tc = False
     if tc and not decode:
         _need(blocks, "blocks", torch.int32, (None, 4))
-        _check(L.jb_attn_tc_prefill_ext(_p(q), _p(k_cache), _p(v_cache),
+        _check(L.jb_attn_tc_prefill_gen(_p(q), _p(k_cache), _p(v_cache),
                                         int(k_cache.shape[0]), _p(blocks),
                                         blocks.shape[0], _p(block_table), block_table.shape[1],
                                         _p(out), n, nh, nkv, hd, window, float(scale),
                                         _p(head_scale), _p(sink), float(softcap), _p(slopes),
-                                        _stream()),
+                                        int(keep_first), _p(score_bias), _stream()),
                "attention (tcgen05, prefill)")
         return out
+    kc = int(L.jb_attention_kept_chunks(window, int(keep_first)))
     if tc:
-        # CTAs per (token, KV head): each runs over per_cta chunks and leaves one partial
+        # CTAs per (token, KV head): each runs over per_cta chunks and leaves one partial;
+        # the kept first tokens' chunks are a CTA and a partial each, before the others
+        win = max(max_chunks - kc, 1)
         if L.jb_attn_tc_decode_runs(nh, nkv, hd):
-            parts = _decode_parts(min(n, 4096) * nkv, max_chunks, 2 * _sm_count(q.device))
+            parts = _decode_parts(min(n, 4096) * nkv, win, 2 * _sm_count(q.device))
         else:
-            parts = max_chunks
-        per_cta = (max_chunks + parts - 1) // parts
-        parts = (max_chunks + per_cta - 1) // per_cta
+            parts = win
+        per_cta = (win + parts - 1) // parts
+        parts = kc + (win + per_cta - 1) // per_cta
     else:
         parts, per_cta = max_chunks, 1
     per_row = int(L.jb_attention_scratch(1, nh, vd, parts))
@@ -767,16 +778,18 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     for row0 in range(0, n, rows_per_call):
         cnt = min(rows_per_call, n - row0)
         if tc:
-            _check(L.jb_attn_tc_decode_ext(_p(q), _p(k_cache), _p(v_cache),
+            _check(L.jb_attn_tc_decode_gen(_p(q), _p(k_cache), _p(v_cache),
                                            int(k_cache.shape[0]), _p(row_pos),
                                            _p(row_seq), _p(block_table), block_table.shape[1],
                                            _p(scratch), n, row0, cnt, nh, nkv, hd, window,
                                            float(scale), _p(head_scale), float(softcap),
-                                           _p(slopes), max_chunks, per_cta, _stream()),
+                                           _p(slopes), int(keep_first), _p(score_bias),
+                                           max(max_chunks, kc + 1), per_cta, _stream()),
                    "attention (tcgen05, decode)")
-            _check(L.jb_attention_merge_sink(_p(scratch), _p(row_pos), _p(out), _DT[q.dtype], row0,
-                                             cnt, nh, hd, window, parts, per_cta, _p(sink),
-                                             _stream()), "attention merge")
+            _check(L.jb_attention_merge_gen(_p(scratch), _p(row_pos), _p(out), _DT[q.dtype], row0,
+                                            cnt, nh, hd, window, parts, per_cta, _p(sink),
+                                            int(keep_first), 1 if score_bias is not None else 0,
+                                            _stream()), "attention merge")
         else:
             _check(L.jb_attention_gen(_p(q), _p(k_cache), _p(v_cache), _DT[q.dtype], _p(row_pos),
                                       _p(row_seq), _p(block_table), block_table.shape[1],

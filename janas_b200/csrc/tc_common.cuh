@@ -239,6 +239,15 @@ __device__ __forceinline__ float fast_exp2(float x)
     return y;
 }
 
+// 1 / (1 + 2^-x): a sigmoid of a score in log2 units, by the hardware's approximate
+// exponential and reciprocal (2^-x = inf gives 0)
+__device__ __forceinline__ float fast_sigmoid2(float x)
+{
+    float e = fast_exp2(-x), y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(1.0f + e));
+    return y;
+}
+
 // A barrier among `count` threads of the CTA (count a multiple of 32), by number.
 __device__ __forceinline__ void named_barrier(int id, int count)
 {

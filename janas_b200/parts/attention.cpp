@@ -419,7 +419,7 @@ public:
     const int32_t *prefill_blocks(StepContext &ctx, bool decode) {
         n_blocks_ = 0;
         if (decode || ctx.dtype != BF16 || !ops::attention_tc_ok(g_.nh, g_.nkv, g_.hd) || g_.vd != g_.hd ||
-            (head_scale_ && !g_.head_scale_positive) || g_.keep_first || score_bias_ || ctx.seq_len.empty())
+            (head_scale_ && !g_.head_scale_positive) || ctx.seq_len.empty())
             return nullptr;
         int per = ops::attention_block_positions(g_.nh, g_.nkv);
         std::string key = "attention_blocks/" + std::to_string(per);

@@ -165,7 +165,7 @@ def relu2_expert(h, up, down, rounding=None):
     return _round(a, rounding) @ down.T
 
 
-def route(logits: torch.Tensor, correction: torch.Tensor, r: dict):
+def route(logits: torch.Tensor, correction: torch.Tensor, r: dict, margin: Optional[list] = None):
     """One token's router logits -> (chosen indices, weights)."""
     n = logits.shape[0]
     s = torch.softmax(logits, dim=0)
@@ -176,17 +176,26 @@ def route(logits: torch.Tensor, correction: torch.Tensor, r: dict):
     gscore = [max(choice[g * per:(g + 1) * per].tolist()) for g in range(count)]
     best = sorted(range(count), key=lambda g: (-gscore[g], g))[:keep]
     allowed = [e for e in range(n) if e // per in best]
-    chosen = sorted(allowed, key=lambda e: (-float(choice[e]), e))[:r["top"]]
+    ranked = sorted(allowed, key=lambda e: (-float(choice[e]), e))
+    chosen = ranked[:r["top"]]
+    if margin is not None:
+        # how far the choice is from another one: the gap between the last kept group and the
+        # next, and between the last chosen output and the next allowed one
+        gs = sorted(gscore, reverse=True)
+        gaps = [gs[keep - 1] - gs[keep]] if keep < count else []
+        if len(ranked) > r["top"]:
+            gaps.append(float(choice[ranked[r["top"] - 1]] - choice[ranked[r["top"]]]))
+        margin.append(min(gaps) if gaps else float("inf"))
     return chosen, [float(s[e]) * r["scale"] for e in chosen]
 
 
-def moe(h, w, pre, mlp, rounding=None):
+def moe(h, w, pre, mlp, rounding=None, margin=None):
     r = mlp["router"]
     E, ident = r["experts"], r.get("identity", 0)
     logits = h @ w[pre + "router"].T                 # [T, E + ident]
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
-        chosen, weights = route(logits[t], w[pre + "correction"], r)
+        chosen, weights = route(logits[t], w[pre + "correction"], r, margin)
         for e, wt in zip(chosen, weights):
             if e >= E:
                 out[t] += wt * h[t]
@@ -198,8 +207,9 @@ def moe(h, w, pre, mlp, rounding=None):
 
 
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], rounding: Optional[str] = None,
-            trace: Optional[list] = None) -> torch.Tensor:
-    """All logits [T, vocab] of one sequence; trace gets the residual stream after every layer."""
+            trace: Optional[list] = None, margins: Optional[list] = None) -> torch.Tensor:
+    """All logits [T, vocab] of one sequence; trace gets the residual stream after every layer,
+    margins one list per routed feed-forward: for every token, how close its choice was."""
     eps = cfg["norm"]["eps"]
     canon = cfg.get("canon")
     x = w["embed"][torch.tensor(tokens)] * cfg["embedding"]["scale"]
@@ -217,7 +227,11 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], rounding: 
         if layer.get("mlp"):
             h = short_conv(x, w[p + "canon2"]) if canon else x
             h = _round(h, rounding)
-            x = x + layer_norm_nobias(moe(h, w, p + "mlp.", layer["mlp"], rounding), w[p + "norm2"], eps)
+            margin = None
+            if margins is not None:
+                margin = []
+                margins.append(margin)
+            x = x + layer_norm_nobias(moe(h, w, p + "mlp.", layer["mlp"], rounding, margin), w[p + "norm2"], eps)
         if trace is not None:
             trace.append(x.clone())
     h = _round(layer_norm_nobias(x, w["final.norm"], eps), rounding)

@@ -103,7 +103,8 @@ def test_short_convolution_over_time(odt, taps, dm):
         args = (x.to(DEV), w.to(DEV), state, row_pos.to(DEV), row_seq.to(DEV), sl.slot.to(DEV), odt)
         if split:
             got = ops().short_conv(*args, write_h=True, write_state=False)
-            ops().short_conv(*args, write_h=False, write_state=True)
+            if taps > 1:
+                ops().short_conv(*args, write_h=False, write_state=True)
         else:
             got = ops().short_conv(*args)
         ref = torch.cat([want[i][p0:p0 + cnt] for i, (p0, cnt) in enumerate(rows)])
@@ -380,7 +381,8 @@ def run_sigmoid_attention(dtype, hd, vd, nh, nkv, lens, rows, window=0, keep=0, 
     chunk = ops().attention_chunk()
     max_chunks = int(row_pos.max()) // chunk + 1
     if window:
-        max_chunks = min(max_chunks, (window - 1) // chunk + 2 + ops().attention_kept_chunks(window, keep))
+        # the kept tokens' chunks come first among a row's partial results, always
+        max_chunks = min(max_chunks, (window - 1) // chunk + 2) + ops().attention_kept_chunks(window, keep)
     kw = {}
     if mode == "plain":
         kw["force_simt"] = True
@@ -441,7 +443,8 @@ def test_the_weights_are_not_normalized():
     for qp, window, keep, seen in [(89, 0, 0, 90), (89, 30, 0, 30), (89, 30, 7, 37), (20, 30, 7, 21), (33, 30, 7, 34),
                                    (40, 30, 70, 41)]:
         got = ops().attention(q.to(DEV), P.fill([k], 1, 16, torch.float32), P.fill([v], 1, 16, torch.float32),
-                              i32([qp]), i32([0]), P.table.to(DEV), window, 1.0, 2, keep_first=keep,
+                              i32([qp]), i32([0]), P.table.to(DEV), window, 1.0,
+                              (2 if window else 1) + ops().attention_kept_chunks(window, keep), keep_first=keep,
                               score_bias=torch.tensor([0.0, math.log(3.0)]).to(DEV)).cpu()
         assert abs(float(got[0, 0, 0]) - 0.5 * seen) <= 1e-4, (qp, window, keep)
         assert abs(float(got[0, 1, 0]) - 0.75 * seen) <= 1e-4       # the head's bias: sigmoid(ln 3) = 3/4
@@ -484,6 +487,19 @@ def test_keys_at_the_edges_of_the_window_and_of_the_kept_tokens(dtype, mode, hd,
             close(got, want, dtype, f"window {window} keep {keep} query {qp} key {kp}")
 
 
+@pytest.mark.parametrize("window,keep", [(600, 130), (300, 3), (0, 0)])
+def test_many_decoded_rows_share_the_device(window, keep):
+    """With many rows a block of the tensor-core decode kernel runs over several chunks and
+    leaves one partial result for them; the kept tokens' chunks stay partial results of their own."""
+    lens = [640 + 3 * i for i in range(40)]
+    rows = [(n - 1, 1) for n in lens]
+    pb = torch.full((4,), -5.0)
+    got, want = run_sigmoid_attention(torch.bfloat16, 128, 128, 4, 2, lens, rows, window, keep, seed=8,
+                                      standout=[(7, 2, lens[7] - 1), (9, 131, lens[9] - 1), (11, 300, lens[11] - 1)],
+                                      decode=True, mode="tc", pb=pb)
+    close(got, want, torch.bfloat16)
+
+
 # ------------------------------------------------------------------ whole models
 LENGTHS = {"KA": [1, 2, 9, 70, 131, 260], "KB": [1, 3, 64, 65, 200, 410], "KC": [2, 17, 128, 129, 300, 520],
            "KD": [1, 5, 33, 64, 190, 330], "KE": [1, 2, 4, 30, 66, 140]}
@@ -508,11 +524,19 @@ def engine(name, dtype, max_tokens=2048):
 _PLAIN = {}
 
 
+CLOSE_CALL = 1e-2
+
+
 def plain_logits(name, toks, rounding=None):
+    """The plain model's logits, and for every position how close the closest choice of any of
+    its routers was (the gap between the last chosen score and the next)."""
     key = (name, tuple(toks), rounding)
     if key not in _PLAIN:
         _, c, w = model(name)
-        _PLAIN[key] = pk.forward(c, w, list(toks), rounding).numpy()
+        margins = []
+        logits = pk.forward(c, w, list(toks), rounding, None, margins).numpy()
+        m = np.asarray(margins, dtype=np.float64).reshape(-1, len(toks))
+        _PLAIN[key] = (logits, m.min(0) if len(m) else np.full(len(toks), np.inf))
     return _PLAIN[key]
 
 
@@ -520,11 +544,23 @@ def check(name, dtype, got, reqs, ids):
     for rid, toks in zip(ids, reqs):
         have = np.stack([got[rid][p] for p in range(len(toks))])
         if dtype == "float32":
-            e = rel_err(have, plain_logits(name, toks))
+            e = rel_err(have, plain_logits(name, toks)[0])
             assert e <= FP32_TOL, f"{name} {rid} len {len(toks)}: {e:.3e}"
         else:
-            e = rel_err(have, plain_logits(name, toks, "bfloat16"))
-            assert e <= BF16_TOL, f"{name} {rid} len {len(toks)}: {e:.3e}"
+            # with 16-bit products a router's two scores that are closer than their rounding can
+            # change places; such a token takes another expert in either implementation, and
+            # that is no fault.  Sixteen-bit rounding moves a choice score by a few thousandths
+            # here, so tokens whose closest call is nearer than CLOSE_CALL are left out of the
+            # comparison (a minority, counted below); all others are held to the limit, and the
+            # float32 runs hold every token to theirs.
+            want, margin = plain_logits(name, toks, "bfloat16")
+            assert np.isfinite(have).all()
+            err = np.abs(have - want).max(1) / np.abs(want).max()
+            sure = margin >= CLOSE_CALL
+            assert (~sure).sum() <= max(1, len(toks) // 3), f"{name} {rid}: {(~sure).sum()} close calls"
+            assert (err[sure] <= BF16_TOL).all(), \
+                f"{name} {rid} len {len(toks)}: {err[sure].max():.3e} at {np.nonzero(sure & (err > BF16_TOL))[0].tolist()}"
+            assert (err <= 0.5).all(), f"{name} {rid}: {err.max():.3e}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -578,7 +614,7 @@ def test_every_part_shows():
                lambda d, ww: d["layers"][0]["mlp"]["router"].update(identity=0, experts=8),
                lambda d, ww: d["layers"][0]["mlp"]["router"]["groups"].update(keep=4),
                lambda d, ww: d["layers"][1]["mlp"]["router"].update(top=2),
-               lambda d, ww: d["layers"][2]["mlp"]["router"].update(scale=1.0),
+               lambda d, ww: d["layers"][0]["mlp"]["router"].update(scale=1.0),
                no("mix.pb"), no(".correction"), no("mix.z.b"), no("mix.q.b"), no("canon2"), no("shared.down")]
     for i, change in enumerate(changes):
         d, ww = copy.deepcopy(c), dict(w)
