@@ -185,6 +185,79 @@ norm_residual_kernel(float *__restrict__ x, const float *__restrict__ a, int Sa,
         xr[i] += fmaf((row[i] - mean) * inv, w[i], bias != nullptr ? bias[i] : 0.0f);
 }
 
+// The same for rows of up to 1024 NV values, a multiple of four, with every pointer on a
+// 16-byte boundary: a thread keeps its values of the row in registers, four to a load, and
+// x is read and written once.  The sums run in the same order as above within a thread.
+template <typename TS, int NV>
+__global__ void __launch_bounds__(256)
+norm_residual_vec_kernel(float *__restrict__ x, const float *__restrict__ a, int Sa, size_t a_stride,
+                         const float *__restrict__ a_bias, const TS *__restrict__ skip,
+                         const float *__restrict__ coef, int coef_ld, const float *__restrict__ w,
+                         const float *__restrict__ bias, int dm, float eps, int rms)
+{
+    __shared__ float red[32];
+    pdl_trigger();
+    int r = blockIdx.x;
+    int nv = dm / 4;
+    // the weights were there long before the kernel before this one
+    float4 wv[NV];
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        int i = threadIdx.x + k * 256;
+        wv[k] = i < nv ? load4(w + 4 * i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    pdl_wait();
+    float c = skip != nullptr ? coef[(size_t)r * coef_ld] : 0.0f;
+    float4 v[NV];
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        int i = threadIdx.x + k * 256;
+        float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (i < nv) {
+            if (a_bias != nullptr)
+                t = load4(a_bias + 4 * i);
+            const float *p = a + (size_t)r * dm + 4 * i;
+            for (int sp = 0; sp < Sa; sp++) {
+                float4 u = load4(p + (size_t)sp * a_stride);
+                t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+            }
+            if (skip != nullptr) {
+                float4 u = load4(skip + (size_t)r * dm + 4 * i);
+                t.x = fmaf(c, u.x, t.x); t.y = fmaf(c, u.y, t.y);
+                t.z = fmaf(c, u.z, t.z); t.w = fmaf(c, u.w, t.w);
+            }
+            sum += (t.x + t.y) + (t.z + t.w);
+        }
+        v[k] = t;
+    }
+    float mean = rms ? 0.0f : block_sum(sum, red) / (float)dm;
+    float sq = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        if (threadIdx.x + k * 256 < nv) {
+            float dx = v[k].x - mean, dy = v[k].y - mean, dz = v[k].z - mean, dw = v[k].w - mean;
+            sq = fmaf(dx, dx, sq); sq = fmaf(dy, dy, sq); sq = fmaf(dz, dz, sq); sq = fmaf(dw, dw, sq);
+        }
+    }
+    float var = block_sum(sq, red) / (float)dm;
+    float inv = 1.0f / sqrtf(var + eps);
+    float *xr = x + (size_t)r * dm;
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        int i = threadIdx.x + k * 256;
+        if (i < nv) {
+            float4 b = bias != nullptr ? load4(bias + 4 * i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            float4 o = load4(xr + 4 * i);
+            o.x += fmaf((v[k].x - mean) * inv, wv[k].x, b.x);
+            o.y += fmaf((v[k].y - mean) * inv, wv[k].y, b.y);
+            o.z += fmaf((v[k].z - mean) * inv, wv[k].z, b.z);
+            o.w += fmaf((v[k].w - mean) * inv, wv[k].w, b.w);
+            store4(xr + 4 * i, o);
+        }
+    }
+}
+
 // The same for few rows of the bfloat16 path: a cluster of C CTAs per row (see
 // layernorm_cluster_kernel).
 template <typename TS, int C>
@@ -274,12 +347,33 @@ extern "C" int jb_norm_residual(float *x, const float *a, int Sa, long long a_st
             launch(norm_residual_kernel<TS>, (unsigned)n, threads, (size_t)dm * 4, st, x, a, Sa,        \
                    (size_t)a_stride, a_bias, (const TS *)skip, coef, coef_ld, w, bias, dm, eps, rms);   \
     } while (0)
-    if (skip == nullptr || skip_dt == JB_F32)
-        JB_NR(float);
-    else if (skip_dt == JB_BF16)
-        JB_NR(bf16);
-    else
+    // rows of a multiple of four values on 16-byte boundaries: the kernel that keeps a row in
+    // registers (chosen by the row's size and the addresses alone, never by the batch)
+    auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    bool vec = !cluster && dm % 4 == 0 && dm <= 8192 && al16(x) && al16(a) && al16(a_bias) && al16(skip) &&
+               al16(w) && al16(bias) && a_stride % 4 == 0;
+#define JB_NRV(TS, NV)                                                                                  \
+    launch(norm_residual_vec_kernel<TS, NV>, (unsigned)n, 256, 0, st, x, a, Sa, (size_t)a_stride, a_bias, \
+           (const TS *)skip, coef, coef_ld, w, bias, dm, eps, rms)
+#define JB_NRV_ANY(TS)                                                                                  \
+    do {                                                                                                \
+        if (dm <= 1024) JB_NRV(TS, 1);                                                                  \
+        else if (dm <= 2048) JB_NRV(TS, 2);                                                             \
+        else if (dm <= 4096) JB_NRV(TS, 4);                                                             \
+        else JB_NRV(TS, 8);                                                                             \
+    } while (0)
+    if (skip != nullptr && skip_dt != JB_F32 && skip_dt != JB_BF16)
         return JB_EINVAL;
+    if (vec && (skip == nullptr || skip_dt == JB_F32))
+        JB_NRV_ANY(float);
+    else if (vec)
+        JB_NRV_ANY(bf16);
+    else if (skip == nullptr || skip_dt == JB_F32)
+        JB_NR(float);
+    else
+        JB_NR(bf16);
+#undef JB_NRV_ANY
+#undef JB_NRV
 #undef JB_NR
     return launch_status();
 }

@@ -73,6 +73,77 @@ short_conv_kernel(const float *__restrict__ x, const float *__restrict__ w, floa
     }
 }
 
+// The same for 2 to 4 taps and a multiple of four channels, with x, the state and out on
+// 16-byte boundaries: a thread has four channels of RB consecutive rows.  It keeps the last
+// taps - 1 inputs in registers and moves along the rows, so that a row of x is read once
+// (and the ones before a thread's first row once more); where a row starts a sequence's part
+// of the step the inputs before it come from the state (or are zero before position 0).
+template <typename TO, int TAPS, int RB>
+__global__ void __launch_bounds__(256)
+short_conv_rows_kernel(const float *__restrict__ x, const float *__restrict__ w, float *__restrict__ state,
+                       size_t slot_stride, const int32_t *__restrict__ row_pos,
+                       const int32_t *__restrict__ row_seq, const int32_t *__restrict__ seq_slot,
+                       TO *__restrict__ out, int n, int dm, int what)
+{
+    constexpr int KEEP = TAPS - 1;
+    pdl_trigger();
+    int per_row = dm / 4;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int rb = (int)(idx / per_row), c = (int)(idx - (size_t)rb * per_row) * 4;
+    int r0 = rb * RB, r1 = min(n, r0 + RB);
+    if (r0 >= n)
+        return;
+    // wt[j]: tap j of the thread's four channels
+    float4 wt[TAPS];
+#pragma unroll
+    for (int j = 0; j < TAPS; j++)
+        wt[j] = make_float4(w[(size_t)c * TAPS + j], w[(size_t)(c + 1) * TAPS + j],
+                            w[(size_t)(c + 2) * TAPS + j], w[(size_t)(c + 3) * TAPS + j]);
+    pdl_wait();
+    float4 hist[KEEP];          // hist[k - 1]: the input k positions back
+    int prev_seq = -1;
+#pragma unroll 1
+    for (int r = r0; r < r1; r++) {
+        int pos = row_pos[r], seq = row_seq[r];
+        float *st = state + (size_t)seq_slot[seq] * slot_stride;
+        if (r == r0 || seq != prev_seq) {
+#pragma unroll
+            for (int k = 1; k <= KEEP; k++) {
+                int p = pos - k;
+                if (p < 0)
+                    hist[k - 1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                else if (r - k >= 0 && row_seq[r - k] == seq)
+                    hist[k - 1] = load4(x + (size_t)(r - k) * dm + c);
+                else
+                    hist[k - 1] = load4(st + (size_t)(p % KEEP) * dm + c);
+            }
+        }
+        prev_seq = seq;
+        float4 cur = load4(x + (size_t)r * dm + c);
+        if (what & 1) {
+            float4 acc;
+            acc.x = fmaf(wt[KEEP].x, cur.x, cur.x);
+            acc.y = fmaf(wt[KEEP].y, cur.y, cur.y);
+            acc.z = fmaf(wt[KEEP].z, cur.z, cur.z);
+            acc.w = fmaf(wt[KEEP].w, cur.w, cur.w);
+#pragma unroll
+            for (int k = 1; k <= KEEP; k++) {
+                acc.x = fmaf(wt[KEEP - k].x, hist[k - 1].x, acc.x);
+                acc.y = fmaf(wt[KEEP - k].y, hist[k - 1].y, acc.y);
+                acc.z = fmaf(wt[KEEP - k].z, hist[k - 1].z, acc.z);
+                acc.w = fmaf(wt[KEEP - k].w, hist[k - 1].w, acc.w);
+            }
+            store4(out + (size_t)r * dm + c, acc);
+        }
+        if ((what & 2) && (r + KEEP >= n || row_seq[r + KEEP] != seq))
+            store4(st + (size_t)(pos % KEEP) * dm + c, cur);
+#pragma unroll
+        for (int k = KEEP - 1; k > 0; k--)
+            hist[k] = hist[k - 1];
+        hist[0] = cur;
+    }
+}
+
 // ---------------------------------------------------------------------- minGRU
 //
 //   z = sigmoid(P_z + b_z);  u = P_x + b_x;  c = u + 1/2 (u >= 0), sigmoid(u) (u < 0)
@@ -92,15 +163,38 @@ struct GruIn {
 
 __device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + expf(-v)); }
 
-// a_t = 1 - z_t, b_t = z_t c_t of (row, channel)
-__device__ __forceinline__ void gru_coef(const GruIn &in, int r, int ch, float &a, float &b)
+
+
+// a_t = 1 - z_t, b_t = z_t c_t from the gates' sums (bias included)
+__device__ __forceinline__ void gru_coef(float zs, float u, float &a, float &b)
 {
-    const float *p = in.P + (size_t)r * in.ld + in.col0 + ch;
-    float z = sigmoidf_(add_partials(in.bias != nullptr ? in.bias[ch] : 0.0f, p, in.S, in.stride));
-    float u = add_partials(in.bias != nullptr ? in.bias[in.W + ch] : 0.0f, p + in.W, in.S, in.stride);
+    float z = sigmoidf_(zs);
     float c = u >= 0.0f ? u + 0.5f : sigmoidf_(u);
     a = 1.0f - z;
     b = z * c;
+}
+
+// GRU_U: rows whose gates a thread of the minGRU kernels computes together (8 along a piece,
+// 1 where every row is a piece of its own).
+// The sums of column block `blk` (0 z, 1 x, 2 g) of channel ch for the GRU_U rows from rb on
+// (rows past r1 - 1 repeat that row: nothing branches, so the loads go out together).
+template <int GRU_U>
+__device__ __forceinline__ void gru_sums(const GruIn &in, int blk, int rb, int r1, int ch, float *out)
+{
+    float bias = in.bias != nullptr ? in.bias[blk * in.W + ch] : 0.0f;
+    const float *p = in.P + in.col0 + (size_t)blk * in.W + ch;
+    if (in.S == 1) {
+#pragma unroll
+        for (int u = 0; u < GRU_U; u++)
+            out[u] = p[(size_t)min(rb + u, r1 - 1) * in.ld];
+#pragma unroll
+        for (int u = 0; u < GRU_U; u++)
+            out[u] += bias;
+    } else {
+#pragma unroll
+        for (int u = 0; u < GRU_U; u++)
+            out[u] = add_partials(bias, p + (size_t)min(rb + u, r1 - 1) * in.ld, in.S, in.stride);
+    }
 }
 
 // Rows are cut into pieces of `piece` consecutive rows of the step; a thread owns one
@@ -108,6 +202,7 @@ __device__ __forceinline__ void gru_coef(const GruIn &in, int r, int ch, float &
 // sequence within the step starts from the slot's state instead (A = 0).  This kernel
 // leaves A and B of every piece in AB [pieces, 2, W] and a copy of the state each
 // sequence starts from in init [sequences, W].
+template <int GRU_U>
 __global__ void __launch_bounds__(128)
 mingru_pieces_kernel(GruIn in, const float *__restrict__ state, const int32_t *__restrict__ row_seq,
                      const int32_t *__restrict__ seq_slot, float *__restrict__ AB, float *__restrict__ init,
@@ -120,19 +215,35 @@ mingru_pieces_kernel(GruIn in, const float *__restrict__ state, const int32_t *_
     pdl_wait();
     int r0 = pc * piece, r1 = min(n, r0 + piece);
     float A = 1.0f, B = 0.0f;
-    for (int r = r0; r < r1; r++) {
-        float a, b;
-        gru_coef(in, r, ch, a, b);
-        int seq = row_seq[r];
-        if (r == 0 || row_seq[r - 1] != seq) {
-            float s0 = state[(size_t)seq_slot[seq] * in.W + ch];
-            init[(size_t)seq * in.W + ch] = s0;
-            A = 0.0f;
-            B = fmaf(a, s0, b);
-        } else {
-            A *= a;
-            B = fmaf(a, B, b);
-        }
+    // GRU_U rows at a time: their gates are fetched and computed together, so that the chain
+    // through the rows is one of multiply-adds, not of memory latencies
+    int before = r0 > 0 ? row_seq[r0 - 1] : -1;
+    for (int rb = r0; rb < r1; rb += GRU_U) {
+        float a[GRU_U], b[GRU_U];
+        int sq[GRU_U];
+        gru_sums<GRU_U>(in, 0, rb, r1, ch, a);
+        gru_sums<GRU_U>(in, 1, rb, r1, ch, b);
+#pragma unroll
+        for (int u = 0; u < GRU_U; u++)
+            sq[u] = row_seq[min(rb + u, r1 - 1)];
+#pragma unroll
+        for (int u = 0; u < GRU_U; u++)
+            gru_coef(a[u], b[u], a[u], b[u]);
+#pragma unroll
+        for (int u = 0; u < GRU_U; u++)
+            if (rb + u < r1) {
+                int seq = sq[u];
+                if (seq != before) {
+                    float s0 = state[(size_t)seq_slot[seq] * in.W + ch];
+                    init[(size_t)seq * in.W + ch] = s0;
+                    A = 0.0f;
+                    B = fmaf(a[u], s0, b[u]);
+                } else {
+                    A *= a[u];
+                    B = fmaf(a[u], B, b[u]);
+                }
+                before = seq;
+            }
     }
     AB[((size_t)pc * 2) * in.W + ch] = A;
     AB[((size_t)pc * 2 + 1) * in.W + ch] = B;
@@ -159,7 +270,7 @@ mingru_carry_kernel(const float *__restrict__ AB, float *__restrict__ carry, int
 // output and the new state.  init null: a sequence's start is read from the state
 // itself (only where the thread that reads it is the one that writes it: one piece, or
 // one row per sequence).
-template <typename TO>
+template <typename TO, int GRU_U>
 __global__ void __launch_bounds__(128)
 mingru_scan_kernel(GruIn in, float *__restrict__ state, const int32_t *__restrict__ row_seq,
                    const int32_t *__restrict__ seq_slot, const float *__restrict__ carry,
@@ -172,18 +283,36 @@ mingru_scan_kernel(GruIn in, float *__restrict__ state, const int32_t *__restric
     pdl_wait();
     int r0 = pc * piece, r1 = min(n, r0 + piece);
     float s = carry != nullptr ? carry[(size_t)pc * in.W + ch] : 0.0f;
-    for (int r = r0; r < r1; r++) {
-        float a, b;
-        gru_coef(in, r, ch, a, b);
-        int seq = row_seq[r];
-        if (r == 0 || row_seq[r - 1] != seq)
-            s = init != nullptr ? init[(size_t)seq * in.W + ch] : state[(size_t)seq_slot[seq] * in.W + ch];
-        s = fmaf(a, s, b);
-        float g = add_partials(in.bias != nullptr ? in.bias[2 * in.W + ch] : 0.0f,
-                               in.P + (size_t)r * in.ld + in.col0 + 2 * in.W + ch, in.S, in.stride);
-        out[(size_t)r * in.W + ch] = from_f<TO>(s * (g * sigmoidf_(g)));
-        if (r + 1 == n || row_seq[r + 1] != seq)
-            state[(size_t)seq_slot[seq] * in.W + ch] = s;
+    int before = r0 > 0 ? row_seq[r0 - 1] : -1;
+    for (int rb = r0; rb < r1; rb += GRU_U) {
+        float a[GRU_U], b[GRU_U], gs[GRU_U];
+        int sq[GRU_U + 1];
+        gru_sums<GRU_U>(in, 0, rb, r1, ch, a);
+        gru_sums<GRU_U>(in, 1, rb, r1, ch, b);
+        gru_sums<GRU_U>(in, 2, rb, r1, ch, gs);
+#pragma unroll
+        for (int u = 0; u < GRU_U; u++)
+            sq[u] = row_seq[min(rb + u, r1 - 1)];
+#pragma unroll
+        for (int u = 0; u < GRU_U; u++) {
+            gru_coef(a[u], b[u], a[u], b[u]);
+            gs[u] = gs[u] * sigmoidf_(gs[u]);
+        }
+        int last = min(GRU_U, r1 - rb);
+        int after = rb + last < n ? row_seq[rb + last] : -1;
+#pragma unroll
+        for (int u = 0; u < GRU_U; u++)
+            if (rb + u < r1) {
+                int r = rb + u, seq = sq[u];
+                if (seq != before)
+                    s = init != nullptr ? init[(size_t)seq * in.W + ch] : state[(size_t)seq_slot[seq] * in.W + ch];
+                s = fmaf(a[u], s, b[u]);
+                out[(size_t)r * in.W + ch] = from_f<TO>(s * gs[u]);
+                int next = u + 1 < last ? sq[u + 1 < GRU_U ? u + 1 : u] : after;
+                if (next != seq)
+                    state[(size_t)seq_slot[seq] * in.W + ch] = s;
+                before = seq;
+            }
     }
 }
 
@@ -204,6 +333,32 @@ extern "C" int jb_short_conv(const float *x, const float *w, float *state, long 
         ((what & 1) && out == nullptr))
         return JB_EINVAL;
     bool vec = dm % 4 == 0;
+    auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    if (vec && taps >= 2 && taps <= 4 && al16(x) && al16(state) && al16(out) && slot_stride % 4 == 0 &&
+        (out_dt == JB_F32 || out_dt == JB_BF16)) {
+        // many rows: eight to a thread; few: one (a decode step's rows are all of other sequences)
+        bool many = (size_t)n * (dm / 4) >= (size_t)8 * 148 * 1024;
+        int rbs = many ? 8 : 1;
+        size_t threads = (size_t)((n + rbs - 1) / rbs) * (dm / 4);
+        unsigned g = (unsigned)((threads + 255) / 256);
+#define JB_SCR(TO, T, RB)                                                                             \
+    launch(short_conv_rows_kernel<TO, T, RB>, g, 256, 0, st, x, w, state, (size_t)slot_stride, row_pos, \
+           row_seq, seq_slot, (TO *)out, n, dm, what)
+#define JB_SCR_T(TO, RB)                                                                              \
+    do {                                                                                              \
+        if (taps == 2) JB_SCR(TO, 2, RB);                                                             \
+        else if (taps == 3) JB_SCR(TO, 3, RB);                                                        \
+        else JB_SCR(TO, 4, RB);                                                                       \
+    } while (0)
+        if (out_dt == JB_F32) {
+            if (many) JB_SCR_T(float, 8); else JB_SCR_T(float, 1);
+        } else {
+            if (many) JB_SCR_T(bf16, 8); else JB_SCR_T(bf16, 1);
+        }
+#undef JB_SCR_T
+#undef JB_SCR
+        return launch_status();
+    }
     size_t total = (size_t)n * (vec ? dm / 4 : dm);
     unsigned grid = (unsigned)((total + 255) / 256);
 #define JB_SC(TO, V)                                                                                  \
@@ -251,17 +406,23 @@ extern "C" int jb_mingru(const float *P, int S, long long stride, int ld, int co
         if (scratch == nullptr)
             return JB_EINVAL;
         float *AB = scratch, *cr = scratch + (size_t)pieces * 2 * W, *ini = cr + (size_t)pieces * W;
-        launch(mingru_pieces_kernel, grid, 128, 0, st, in, (const float *)state, row_seq, seq_slot, AB, ini, n,
+        launch(mingru_pieces_kernel<8>, grid, 128, 0, st, in, (const float *)state, row_seq, seq_slot, AB, ini, n,
                piece);
         launch(mingru_carry_kernel, (unsigned)((W + 127) / 128), 128, 0, st, (const float *)AB, cr, W, pieces);
         carry = cr;
         init = ini;
     }
-    if (out_dt == JB_F32)
-        launch(mingru_scan_kernel<float>, grid, 128, 0, st, in, state, row_seq, seq_slot, carry, init,
+    if (out_dt == JB_F32 && piece == 1)
+        launch(mingru_scan_kernel<float, 1>, grid, 128, 0, st, in, state, row_seq, seq_slot, carry, init,
                (float *)out, n, piece);
+    else if (out_dt == JB_F32)
+        launch(mingru_scan_kernel<float, 8>, grid, 128, 0, st, in, state, row_seq, seq_slot, carry, init,
+               (float *)out, n, piece);
+    else if (piece == 1)
+        launch(mingru_scan_kernel<bf16, 1>, grid, 128, 0, st, in, state, row_seq, seq_slot, carry, init,
+               (bf16 *)out, n, piece);
     else
-        launch(mingru_scan_kernel<bf16>, grid, 128, 0, st, in, state, row_seq, seq_slot, carry, init,
+        launch(mingru_scan_kernel<bf16, 8>, grid, 128, 0, st, in, state, row_seq, seq_slot, carry, init,
                (bf16 *)out, n, piece);
     return launch_status();
 }

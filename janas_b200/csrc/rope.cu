@@ -443,6 +443,98 @@ qkv_prepare_append_kernel(const float *__restrict__ qkv, int S, size_t split_str
     }
 }
 
+// The same for heads of up to 4 L values (L = 8, 16 or 32 lanes to a head slot, four values
+// to a lane) where the head sizes and rot_half are multiples of four and everything lies on
+// 16-byte boundaries (8 for a bfloat16 cache): one load of four sums per lane, the sum of
+// squares over the slot's lanes, and the rotation's partner (rot_half values on, that is
+// rot_half / 4 lanes on) by a shuffle of the finished values.
+template <typename TC, int L>
+__global__ void __launch_bounds__(128)
+qkv_prepare_append_vec_kernel(const float *__restrict__ qkv, int S, size_t split_stride, int ld,
+                              const float *__restrict__ bias, const float *__restrict__ q_w,
+                              const float *__restrict__ k_w, float eps, const float *__restrict__ cs,
+                              const float *__restrict__ sn, int rot_half,
+                              const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
+                              const int32_t *__restrict__ block_table, int bt_stride,
+                              TC *__restrict__ q_out, TC *__restrict__ k_cache, TC *__restrict__ v_cache,
+                              int n, int nh, int nkv, int hd, int vd)
+{
+    constexpr int PER_WARP = 32 / L;
+    pdl_trigger();
+    unsigned slots = nh + 2 * nkv;
+    unsigned total = (unsigned)n * slots;
+    unsigned task = (blockIdx.x * blockDim.y + threadIdx.y) * PER_WARP + threadIdx.x / L;
+    bool live = task < total;
+    if (!live)
+        task = total - 1;          // the lanes stay for the shuffles and store nothing
+    unsigned row = task / slots, hs = task - row * slots;
+    int l = threadIdx.x % L, group0 = threadIdx.x - l;
+    bool is_q = hs < (unsigned)nh;
+    bool is_v = hs >= (unsigned)(nh + nkv);
+    int pos = row_pos[row];
+    int page = k_cache != nullptr ? block_table[(size_t)row_seq[row] * bt_stride + pos / PAGE] : 0;
+    const float *w = is_v ? nullptr : is_q ? q_w : k_w;
+    int len = is_v ? vd : hd;
+    int hl = is_v ? 0 : rot_half / 4;                // lanes to a half of the rotated part
+    size_t col0 = is_q ? (size_t)hs * hd
+                       : !is_v ? (size_t)nh * hd + (size_t)(hs - nh) * hd
+                               : (size_t)(nh + nkv) * hd + (size_t)(hs - nh - nkv) * vd;
+    bool has = 4 * l < len;
+    float4 wv = make_float4(1.0f, 1.0f, 1.0f, 1.0f), co = wv, si = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (w != nullptr && has)
+        wv = load4(w + 4 * l);
+    if (l < 2 * hl) {
+        int f = 4 * (l < hl ? l : l - hl);
+        co = load4(cs + (size_t)pos * rot_half + f);
+        si = load4(sn + (size_t)pos * rot_half + f);
+    }
+    pdl_wait();
+    TC *dst = nullptr;
+    if (is_q) {
+        dst = q_out + ((size_t)row * nh + hs) * hd;
+    } else if (k_cache != nullptr) {
+        int kvh = !is_v ? hs - nh : hs - nh - nkv;
+        size_t at = ((size_t)page * nkv + kvh) * PAGE + (pos % PAGE);
+        dst = !is_v ? k_cache + at * hd : v_cache + at * vd;
+    }
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (has) {
+        const float *src = qkv + (size_t)row * ld + col0 + 4 * l;
+        if (bias != nullptr)
+            v = load4(bias + col0 + 4 * l);
+        for (int sp = 0; sp < S; sp++) {
+            float4 u = load4(src + (size_t)sp * split_stride);
+            v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+        }
+    }
+    float ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+#pragma unroll
+    for (int o = L / 2; o > 0; o >>= 1)
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (w != nullptr) {
+        float scale = 1.0f / sqrtf(ss / (float)len + eps);
+        v.x = (v.x * scale) * wv.x; v.y = (v.y * scale) * wv.y;
+        v.z = (v.z * scale) * wv.z; v.w = (v.w * scale) * wv.w;
+    }
+    if (rot_half > 0) {
+        int pl = group0 + (l < hl ? l + hl : l < 2 * hl ? l - hl : l);
+        float4 u;
+        u.x = __shfl_sync(0xffffffffu, v.x, pl);
+        u.y = __shfl_sync(0xffffffffu, v.y, pl);
+        u.z = __shfl_sync(0xffffffffu, v.z, pl);
+        u.w = __shfl_sync(0xffffffffu, v.w, pl);
+        // (a, b) -> (a cos - b sin, b cos + a sin), a the lower value of the pair
+        if (l < hl)
+            v = make_float4(v.x * co.x - u.x * si.x, v.y * co.y - u.y * si.y, v.z * co.z - u.z * si.z,
+                            v.w * co.w - u.w * si.w);
+        else if (l < 2 * hl)
+            v = make_float4(v.x * co.x + u.x * si.x, v.y * co.y + u.y * si.y, v.z * co.z + u.z * si.z,
+                            v.w * co.w + u.w * si.w);
+    }
+    if (live && has && dst != nullptr)
+        store4(dst + 4 * l, v);
+}
+
 }  // namespace jb
 
 using namespace jb;
@@ -466,8 +558,34 @@ extern "C" int jb_qkv_prepare_append(const float *qkv, int S, long long split_st
     size_t tasks = (size_t)n * (nh + 2 * nkv);
     if (tasks > 0xffffffffu)
         return JB_EINVAL;
-    unsigned grid = (unsigned)((tasks + 3) / 4);
     dim3 block(32, 4);
+    auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    int big = hd > vd ? hd : vd;
+    if (hd % 4 == 0 && vd % 4 == 0 && rot_half % 4 == 0 && big <= 128 && ld % 4 == 0 && split_stride % 4 == 0 &&
+        al16(qkv) && al16(bias) && al16(q_w) && al16(k_w) && al16(cs) && al16(sn) && al16(q_out) &&
+        al16(k_cache) && al16(v_cache) && (cache_dt == JB_F32 || cache_dt == JB_BF16) && tasks > 0) {
+        int L = big <= 32 ? 8 : big <= 64 ? 16 : 32;
+        size_t warps = (tasks + (32 / L) - 1) / (32 / L);
+        unsigned g = (unsigned)((warps + 3) / 4);
+#define JB_QPV(TC, LL)                                                                                  \
+    launch(qkv_prepare_append_vec_kernel<TC, LL>, g, block, 0, st, qkv, S, (size_t)split_stride, ld, bias, \
+           q_w, k_w, eps, cs, sn, rot_half, row_pos, row_seq, block_table, bt_stride, (TC *)q_out,       \
+           (TC *)k_cache, (TC *)v_cache, n, nh, nkv, hd, vd)
+#define JB_QPV_L(TC)                                                                                    \
+    do {                                                                                                \
+        if (L == 8) JB_QPV(TC, 8);                                                                      \
+        else if (L == 16) JB_QPV(TC, 16);                                                               \
+        else JB_QPV(TC, 32);                                                                            \
+    } while (0)
+        if (cache_dt == JB_F32)
+            JB_QPV_L(float);
+        else
+            JB_QPV_L(bf16);
+#undef JB_QPV_L
+#undef JB_QPV
+        return launch_status();
+    }
+    unsigned grid = (unsigned)((tasks + 3) / 4);
     if (cache_dt == JB_F32)
         launch(qkv_prepare_append_kernel<float>, grid, block, 0, st, qkv, S, (size_t)split_stride, ld, bias,
                q_w, k_w, eps, cs, sn, rot_half, row_pos, row_seq, block_table, bt_stride, (float *)q_out,

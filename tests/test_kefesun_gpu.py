@@ -548,19 +548,21 @@ def check(name, dtype, got, reqs, ids):
             assert e <= FP32_TOL, f"{name} {rid} len {len(toks)}: {e:.3e}"
         else:
             # with 16-bit products a router's two scores that are closer than their rounding can
-            # change places; such a token takes another expert in either implementation, and
-            # that is no fault.  Sixteen-bit rounding moves a choice score by a few thousandths
-            # here, so tokens whose closest call is nearer than CLOSE_CALL are left out of the
-            # comparison (a minority, counted below); all others are held to the limit, and the
-            # float32 runs hold every token to theirs.
+            # change places (rounding moves a choice score by a few thousandths here); such a
+            # token takes another expert in either implementation, which is no fault, and the
+            # tokens after it see another key, value and state.  So every token before the
+            # first such close call is held to the limit, and of the ones from there on a
+            # twentieth may be over it (the float32 runs hold every token to theirs).
             want, margin = plain_logits(name, toks, "bfloat16")
             assert np.isfinite(have).all()
             err = np.abs(have - want).max(1) / np.abs(want).max()
-            sure = margin >= CLOSE_CALL
-            assert (~sure).sum() <= max(1, len(toks) // 3), f"{name} {rid}: {(~sure).sum()} close calls"
-            assert (err[sure] <= BF16_TOL).all(), \
-                f"{name} {rid} len {len(toks)}: {err[sure].max():.3e} at {np.nonzero(sure & (err > BF16_TOL))[0].tolist()}"
-            assert (err <= 0.5).all(), f"{name} {rid}: {err.max():.3e}"
+            close_calls = np.nonzero(margin < CLOSE_CALL)[0]
+            first = int(close_calls[0]) if len(close_calls) else len(toks)
+            assert (err[:first] <= BF16_TOL).all(), \
+                f"{name} {rid} len {len(toks)}: {err[:first].max():.3e} at {np.nonzero(err[:first] > BF16_TOL)[0].tolist()}"
+            over = np.nonzero(err[first:] > BF16_TOL)[0] + first
+            assert len(over) <= (len(toks) - first + 19) // 20, f"{name} {rid} len {len(toks)}: over at {over.tolist()}"
+            assert np.median(err) <= BF16_TOL / 5 and (err <= 0.5).all(), f"{name} {rid}: {err.max():.3e}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
