@@ -142,11 +142,10 @@ activation_weighted_kernel(const float *__restrict__ z, int S, size_t stride, in
                            TO *__restrict__ out, int n, int width)
 {
     pdl_trigger();
-    int per_row = width / V;
-    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)n * per_row)
+    // a row of blocks per row of z: no division finds a thread's row
+    int r = blockIdx.x, c = (int)(blockIdx.y * blockDim.x + threadIdx.x) * V;
+    if (c >= width)
         return;
-    int r = (int)(idx / per_row), c = (int)(idx - (size_t)r * per_row) * V;
     pdl_wait();
     int e = c / ff;          // V divides ff when V > 1: the values of a thread are one expert's
     float wgt = e < n_experts ? weights[(size_t)r * w_ld + e] : 1.0f;
@@ -245,8 +244,10 @@ extern "C" int jb_activation_weighted(const float *z, int S, long long stride, i
         return JB_EINVAL;
     bool vec = ff % 4 == 0 && width % 4 == 0 && ld % 4 == 0 && stride % 4 == 0 && (uintptr_t)z % 16 == 0 &&
                (uintptr_t)out % 16 == 0;
-    size_t total = (size_t)n * (vec ? width / 4 : width);
-    unsigned grid = (unsigned)((total + 255) / 256);
+    int per_row = vec ? width / 4 : width;
+    if ((per_row + 255) / 256 > 65535)
+        return JB_EINVAL;
+    dim3 grid((unsigned)n, (unsigned)((per_row + 255) / 256));
 #define JB_AW(TO, V)                                                                                       \
     launch(activation_weighted_kernel<TO, V>, grid, 256, 0, st, z, S, (size_t)stride, ld, weights, w_ld,  \
            n_experts, ff, kind, (TO *)out, n, width)

@@ -102,9 +102,22 @@ short_conv_rows_kernel(const float *__restrict__ x, const float *__restrict__ w,
     pdl_wait();
     float4 hist[KEEP];          // hist[k - 1]: the input k positions back
     int prev_seq = -1;
-#pragma unroll 1
-    for (int r = r0; r < r1; r++) {
-        int pos = row_pos[r], seq = row_seq[r];
+    // the thread's rows are fetched together, then worked through in order
+    float4 in_rows[RB];
+    int in_pos[RB], in_seq[RB];
+#pragma unroll
+    for (int u = 0; u < RB; u++) {
+        int rr = min(r0 + u, r1 - 1);
+        in_rows[u] = load4(x + (size_t)rr * dm + c);
+        in_pos[u] = row_pos[rr];
+        in_seq[u] = row_seq[rr];
+    }
+#pragma unroll
+    for (int u = 0; u < RB; u++) {
+        int r = r0 + u;
+        if (r >= r1)
+            break;
+        int pos = in_pos[u], seq = in_seq[u];
         float *st = state + (size_t)seq_slot[seq] * slot_stride;
         if (r == r0 || seq != prev_seq) {
 #pragma unroll
@@ -119,7 +132,7 @@ short_conv_rows_kernel(const float *__restrict__ x, const float *__restrict__ w,
             }
         }
         prev_seq = seq;
-        float4 cur = load4(x + (size_t)r * dm + c);
+        float4 cur = in_rows[u];
         if (what & 1) {
             float4 acc;
             acc.x = fmaf(wt[KEEP].x, cur.x, cur.x);
@@ -161,15 +174,21 @@ struct GruIn {
     int W;
 };
 
-__device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + expf(-v)); }
+// FAST: the hardware's approximate exponential and division (the bfloat16 path, whose
+// results are rounded to 8 bits of mantissa afterwards); otherwise expf and a true division
+template <bool FAST> __device__ __forceinline__ float sigmoidf_(float v)
+{
+    return FAST ? __fdividef(1.0f, 1.0f + __expf(-v)) : 1.0f / (1.0f + expf(-v));
+}
 
 
 
 // a_t = 1 - z_t, b_t = z_t c_t from the gates' sums (bias included)
+template <bool FAST>
 __device__ __forceinline__ void gru_coef(float zs, float u, float &a, float &b)
 {
-    float z = sigmoidf_(zs);
-    float c = u >= 0.0f ? u + 0.5f : sigmoidf_(u);
+    float z = sigmoidf_<FAST>(zs);
+    float c = u >= 0.0f ? u + 0.5f : sigmoidf_<FAST>(u);
     a = 1.0f - z;
     b = z * c;
 }
@@ -202,7 +221,7 @@ __device__ __forceinline__ void gru_sums(const GruIn &in, int blk, int rb, int r
 // sequence within the step starts from the slot's state instead (A = 0).  This kernel
 // leaves A and B of every piece in AB [pieces, 2, W] and a copy of the state each
 // sequence starts from in init [sequences, W].
-template <int GRU_U>
+template <int GRU_U, bool FAST>
 __global__ void __launch_bounds__(128)
 mingru_pieces_kernel(GruIn in, const float *__restrict__ state, const int32_t *__restrict__ row_seq,
                      const int32_t *__restrict__ seq_slot, float *__restrict__ AB, float *__restrict__ init,
@@ -218,17 +237,29 @@ mingru_pieces_kernel(GruIn in, const float *__restrict__ state, const int32_t *_
     // GRU_U rows at a time: their gates are fetched and computed together, so that the chain
     // through the rows is one of multiply-adds, not of memory latencies
     int before = r0 > 0 ? row_seq[r0 - 1] : -1;
+    // the next rows' sums are asked for before this batch's chain is walked
+    float nz[GRU_U], nu[GRU_U];
+    int nsq[GRU_U];
+    gru_sums<GRU_U>(in, 0, r0, r1, ch, nz);
+    gru_sums<GRU_U>(in, 1, r0, r1, ch, nu);
+#pragma unroll
+    for (int u = 0; u < GRU_U; u++)
+        nsq[u] = row_seq[min(r0 + u, r1 - 1)];
     for (int rb = r0; rb < r1; rb += GRU_U) {
         float a[GRU_U], b[GRU_U];
         int sq[GRU_U];
-        gru_sums<GRU_U>(in, 0, rb, r1, ch, a);
-        gru_sums<GRU_U>(in, 1, rb, r1, ch, b);
 #pragma unroll
-        for (int u = 0; u < GRU_U; u++)
-            sq[u] = row_seq[min(rb + u, r1 - 1)];
+        for (int u = 0; u < GRU_U; u++) {
+            gru_coef<FAST>(nz[u], nu[u], a[u], b[u]);
+            sq[u] = nsq[u];
+        }
+        if (rb + GRU_U < r1) {
+            gru_sums<GRU_U>(in, 0, rb + GRU_U, r1, ch, nz);
+            gru_sums<GRU_U>(in, 1, rb + GRU_U, r1, ch, nu);
 #pragma unroll
-        for (int u = 0; u < GRU_U; u++)
-            gru_coef(a[u], b[u], a[u], b[u]);
+            for (int u = 0; u < GRU_U; u++)
+                nsq[u] = row_seq[min(rb + GRU_U + u, r1 - 1)];
+        }
 #pragma unroll
         for (int u = 0; u < GRU_U; u++)
             if (rb + u < r1) {
@@ -276,6 +307,7 @@ mingru_scan_kernel(GruIn in, float *__restrict__ state, const int32_t *__restric
                    const int32_t *__restrict__ seq_slot, const float *__restrict__ carry,
                    const float *__restrict__ init, TO *__restrict__ out, int n, int piece)
 {
+    constexpr bool FAST = sizeof(TO) == 2;
     pdl_trigger();
     int ch = blockIdx.x * blockDim.x + threadIdx.x, pc = blockIdx.y;
     if (ch >= in.W)
@@ -284,19 +316,31 @@ mingru_scan_kernel(GruIn in, float *__restrict__ state, const int32_t *__restric
     int r0 = pc * piece, r1 = min(n, r0 + piece);
     float s = carry != nullptr ? carry[(size_t)pc * in.W + ch] : 0.0f;
     int before = r0 > 0 ? row_seq[r0 - 1] : -1;
+    // the next rows' sums are asked for before this batch's chain is walked
+    float nz[GRU_U], nu[GRU_U], ng[GRU_U];
+    int nsq[GRU_U];
+    gru_sums<GRU_U>(in, 0, r0, r1, ch, nz);
+    gru_sums<GRU_U>(in, 1, r0, r1, ch, nu);
+    gru_sums<GRU_U>(in, 2, r0, r1, ch, ng);
+#pragma unroll
+    for (int u = 0; u < GRU_U; u++)
+        nsq[u] = row_seq[min(r0 + u, r1 - 1)];
     for (int rb = r0; rb < r1; rb += GRU_U) {
         float a[GRU_U], b[GRU_U], gs[GRU_U];
         int sq[GRU_U + 1];
-        gru_sums<GRU_U>(in, 0, rb, r1, ch, a);
-        gru_sums<GRU_U>(in, 1, rb, r1, ch, b);
-        gru_sums<GRU_U>(in, 2, rb, r1, ch, gs);
-#pragma unroll
-        for (int u = 0; u < GRU_U; u++)
-            sq[u] = row_seq[min(rb + u, r1 - 1)];
 #pragma unroll
         for (int u = 0; u < GRU_U; u++) {
-            gru_coef(a[u], b[u], a[u], b[u]);
-            gs[u] = gs[u] * sigmoidf_(gs[u]);
+            gru_coef<FAST>(nz[u], nu[u], a[u], b[u]);
+            gs[u] = ng[u] * sigmoidf_<FAST>(ng[u]);
+            sq[u] = nsq[u];
+        }
+        if (rb + GRU_U < r1) {
+            gru_sums<GRU_U>(in, 0, rb + GRU_U, r1, ch, nz);
+            gru_sums<GRU_U>(in, 1, rb + GRU_U, r1, ch, nu);
+            gru_sums<GRU_U>(in, 2, rb + GRU_U, r1, ch, ng);
+#pragma unroll
+            for (int u = 0; u < GRU_U; u++)
+                nsq[u] = row_seq[min(rb + GRU_U + u, r1 - 1)];
         }
         int last = min(GRU_U, r1 - rb);
         int after = rb + last < n ? row_seq[rb + last] : -1;
@@ -406,8 +450,12 @@ extern "C" int jb_mingru(const float *P, int S, long long stride, int ld, int co
         if (scratch == nullptr)
             return JB_EINVAL;
         float *AB = scratch, *cr = scratch + (size_t)pieces * 2 * W, *ini = cr + (size_t)pieces * W;
-        launch(mingru_pieces_kernel<8>, grid, 128, 0, st, in, (const float *)state, row_seq, seq_slot, AB, ini, n,
-               piece);
+        if (out_dt == JB_BF16)
+            launch(mingru_pieces_kernel<8, true>, grid, 128, 0, st, in, (const float *)state, row_seq, seq_slot,
+                   AB, ini, n, piece);
+        else
+            launch(mingru_pieces_kernel<8, false>, grid, 128, 0, st, in, (const float *)state, row_seq, seq_slot,
+                   AB, ini, n, piece);
         launch(mingru_carry_kernel, (unsigned)((W + 127) / 128), 128, 0, st, (const float *)AB, cr, W, pieces);
         carry = cr;
         init = ini;
