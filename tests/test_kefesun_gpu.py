@@ -50,7 +50,7 @@ def row_arrays(rows):
 
 # ------------------------------------------------------------ mechanisms alone
 @pytest.mark.parametrize("few", [False, True])
-@pytest.mark.parametrize("n,dm,S", [(1, 50, 1), (7, 256, 3), (130, 1000, 2), (3, 4100, 1), (8, 320, 4)])
+@pytest.mark.parametrize("n,dm,S", [(1, 50, 1), (7, 256, 3), (130, 1000, 2), (3, 4100, 1), (8, 352, 4), (40, 2560, 1), (5, 6000, 2)])
 def test_norm_on_the_result_alone(few, n, dm, S):
     """x += LN(sum of the partial sums + coefficient * the sublayer's input); x itself is not normed."""
     x = rnd(n, dm, scale=3.0) + 2.0
@@ -85,12 +85,15 @@ class Slots:
 
 
 @pytest.mark.parametrize("odt", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("taps,dm", [(4, 320), (2, 50), (5, 136), (3, 1000), (1, 64)])
-def test_short_convolution_over_time(odt, taps, dm):
+@pytest.mark.parametrize("taps,dm,lens", [(4, 352, 0), (2, 50, 0), (5, 136, 0), (3, 1000, 0), (1, 64, 0), (2, 264, 0),
+                                          (4, 2048, [700, 1, 901, 3, 299, 507]), (3, 1536, [1203, 2, 2001])])
+def test_short_convolution_over_time(odt, taps, dm, lens):
     """Whole prompts, then a portion, then rows one by one, against the convolution of the whole
-    sequence: the last inputs are carried in the slots' state."""
-    lens = [1, 9, 2, 70]
-    xs = [rnd(n + 12, dm, seed=10 + i) for i, n in enumerate(lens)]
+    sequence: the last inputs are carried in the slots' state.  The long steps run the kernel
+    whose threads move along several rows, over the sequences' borders."""
+    lens = lens or [1, 9, 2, 70]
+    more = ([2, 1, 5, 3] * 2)[:len(lens)] if max(lens) < 100 else [n + 17 for n in lens]
+    xs = [rnd(n + m + 8, dm, seed=10 + i) for i, (n, m) in enumerate(zip(lens, more))]
     w = rnd(dm, taps, scale=0.5, seed=5)
     want = [pk.short_conv(x, w) for x in xs]
     sl = Slots(len(lens), 7, 3)
@@ -111,8 +114,8 @@ def test_short_convolution_over_time(odt, taps, dm):
         assert (got.float().cpu() - ref).abs().max() <= tol * max(1.0, float(ref.abs().max()))
 
     step([(0, n) for n in lens], False)                               # prompts from position 0
-    step([(n, c) for n, c in zip(lens, (2, 1, 5, 3))], True)          # portions of several sizes
-    at = [n + c for n, c in zip(lens, (2, 1, 5, 3))]
+    step([(n, c) for n, c in zip(lens, more)], True)                  # portions of several sizes
+    at = [n + c for n, c in zip(lens, more)]
     for k in range(4):                                                # one row each
         step([(a + k, 1) for a in at], False)
     if taps > 1:
@@ -134,7 +137,7 @@ def test_a_short_sequence_reads_zeros_before_its_start():
 
 
 @pytest.mark.parametrize("odt", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width,S,extra", [(320, 1, 0), (48, 3, 5), (70, 2, 0), (1000, 1, 8)])
+@pytest.mark.parametrize("width,S,extra", [(352, 1, 0), (48, 3, 5), (70, 2, 0), (1000, 1, 8)])
 def test_mingru_recurrence(odt, width, S, extra):
     """Prompts of unequal length, portions and single rows against the recurrence over the whole
     sequence; the state (float32) is carried per slot."""
@@ -206,7 +209,7 @@ def plain_routes(logits, corr, r):
     return w
 
 
-ROUTERS = [dict(outs=8, ident=2, count=2, keep=1, top=4, scale=2.0),
+ROUTERS = [dict(outs=12, ident=3, count=2, keep=1, top=5, scale=2.2),
            dict(outs=8, ident=2, count=4, keep=2, top=3, scale=1.7),
            dict(outs=3, ident=0, count=1, keep=1, top=1, scale=1.0),
            dict(outs=6, ident=3, count=3, keep=2, top=2, scale=1.2),
@@ -408,7 +411,7 @@ KERNELS = [(torch.float32, "plain", 32, 48), (torch.bfloat16, "plain", 32, 48), 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hd,vd,nh,nkv,window,keep", [(16, 32, 4, 2, 37, 5), (24, 40, 6, 2, 0, 0), (8, 8, 3, 3, 200, 1),
                                                       (64, 64, 4, 1, 130, 64), (128, 128, 2, 2, 64, 130),
-                                                      (128, 64, 4, 2, 96, 6), (16, 16, 2, 1, 1, 2)])
+                                                      (128, 64, 8, 2, 90, 7), (16, 16, 2, 1, 1, 2)])
 def test_sigmoid_attention(dtype, hd, vd, nh, nkv, window, keep):
     lens = [1, 200, 67, 330]
     got, want = run_sigmoid_attention(dtype, hd, vd, nh, nkv, lens, [(0, 1), (0, 200), (60, 7), (329, 1)],
