@@ -81,8 +81,17 @@ KE = config(32, 77, [attn(2, 1, 8, 8, 0.5, window=1, keep=2, rot=(10.0, 2), mlp=
                      gru(24, mlp=moe(2, 16, 2, shared=16))],
             None, eps=1e-5, scale=3.0)
 
-CONFIGS = {"KA": KA, "KB": KB, "KC": KC, "KD": KD, "KE": KE}
-SEEDS = {"KA": 31, "KB": 32, "KC": 33, "KD": 34, "KE": 35}
+# heads of 128 two to a key/value head, a window that crosses a chunk's border with a few kept
+# tokens, half a head rotated (prompts and decoding both on the tensor cores in bfloat16); heads
+# of 64 four to a key/value head that see every key; three taps
+KF = config(144, 190, [attn(4, 2, 128, 128, 0.09, window=150, keep=7, rot=(5000.0, 64),
+                            mlp=moe(5, 48, 2, identity=1, groups=(3, 2), scale=1.4, shared=32)),
+                       attn(8, 2, 64, 64, 0.12, rot=(300.0, 64), mlp=moe(4, 32, 2, groups=(2, 1), scale=1.1)),
+                       gru(144, mlp=moe(3, 56, 1, identity=1, scale=0.9, shared=24))],
+            3, eps=2e-5, scale=6.0)
+
+CONFIGS = {"KA": KA, "KB": KB, "KC": KC, "KD": KD, "KE": KE, "KF": KF}
+SEEDS = {"KA": 31, "KB": 32, "KC": 33, "KD": 34, "KE": 35, "KF": 36}
 
 
 def tensor_shapes(c):

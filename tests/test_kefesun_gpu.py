@@ -505,7 +505,8 @@ def test_many_decoded_rows_share_the_device(window, keep):
 
 # ------------------------------------------------------------------ whole models
 LENGTHS = {"KA": [1, 2, 9, 70, 131, 260], "KB": [1, 3, 64, 65, 200, 410], "KC": [2, 17, 128, 129, 300, 520],
-           "KD": [1, 5, 33, 64, 190, 330], "KE": [1, 2, 4, 30, 66, 140]}
+           "KD": [1, 5, 33, 64, 190, 330], "KE": [1, 2, 4, 30, 66, 140],
+           "KF": [1, 6, 129, 150, 151, 400]}
 FP32_TOL = 3e-5
 BF16_TOL = 5e-2
 _ENGINES = {}
@@ -656,7 +657,7 @@ def trace_portions(reqs, sizes):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["KA", "KB", "KC", "KD"])
+@pytest.mark.parametrize("name", ["KA", "KB", "KC", "KD", "KF"])
 def test_portions(name, dtype):
     """Portions shorter than the convolutions' taps, of a page, over a chunk: the convolutions'
     last inputs and the recurrent state pass from one portion to the next."""
