@@ -423,7 +423,9 @@ def test_sigmoid_attention(dtype, hd, vd, nh, nkv, window, keep):
 
 
 @pytest.mark.parametrize("hd,nh,nkv,window,keep", [(64, 4, 1, 130, 64), (64, 10, 5, 0, 0), (128, 2, 2, 64, 130),
-                                                   (128, 8, 2, 1000, 3), (128, 40, 2, 37, 129), (128, 4, 2, 300, 0)])
+                                                   (128, 8, 2, 1000, 3), (128, 40, 2, 37, 129), (128, 4, 2, 300, 0),
+                                                   (128, 6, 2, 100, 9), (64, 12, 2, 260, 5), (128, 24, 2, 140, 4),
+                                                   (128, 3, 1, 0, 0)])
 def test_sigmoid_attention_on_the_tensor_cores(hd, nh, nkv, window, keep):
     dt = torch.bfloat16
     lens = [1, 300, 131, 1520]
