@@ -152,6 +152,8 @@ class ModelSpec:
     embedding_scale: float = 1.0       # a factor on the embedding rows (a tied head reads the table without it)
     embedding_norm: Optional[PartSpec] = None      # a norm on the embedding rows
     embedding_norm_name: str = "model.embed_norm"
+    token_table_name: str = ""         # a second table of vectors per token that the layers' blocks read; "": none
+    token_table_width: int = 0
 
     def to_json(self) -> Dict[str, Any]:
         d = {
@@ -170,6 +172,9 @@ class ModelSpec:
             d["logit_scale"] = self.logit_scale
         if self.embedding_scale != 1.0:
             d["embedding_scale"] = self.embedding_scale
+        if self.token_table_name:
+            d["token_table_name"] = self.token_table_name
+            d["token_table_width"] = self.token_table_width
         if self.embedding_norm:
             d["embedding_norm"] = self.embedding_norm.to_json()
             d["embedding_norm_name"] = self.embedding_norm_name
@@ -182,6 +187,8 @@ class ModelSpec:
             position_table_name=d.get("position_table_name", ""),
             logit_scale=d.get("logit_scale", 1.0),
             embedding_scale=d.get("embedding_scale", 1.0),
+            token_table_name=d.get("token_table_name", ""),
+            token_table_width=d.get("token_table_width", 0),
             embedding_norm=PartSpec.from_json(d["embedding_norm"]) if d.get("embedding_norm") else None,
             embedding_norm_name=d.get("embedding_norm_name", "model.embed_norm"),
             architecture=d["architecture"], hidden_size=d["hidden_size"],
@@ -313,8 +320,41 @@ class KefesunConfig:
         return hash(json.dumps(self.to_dict(), sort_keys=True))
 
 
+@dataclass(frozen=True)
+class MunisunConfig:
+    """The Munisun decoder's ``config.json`` keys, as the library read them."""
+    vocab: int
+    width: int
+    norm_eps: float
+    embedding_scale: float
+    side_dim: int                             # token_side.dim; 0: no per-layer input of the token itself
+    layers: Tuple[Mapping[str, Any], ...]     # each: type, mixer {left, right, ...}, mlp {...} or None
+    eos_token_ids: Tuple[int, ...] = ()
+    architecture: str = "Munisun"
+    _json: Mapping[str, Any] = field(default_factory=dict, compare=False, repr=False)
+    _spec: Mapping[str, Any] = field(default_factory=dict, compare=False, repr=False)
+
+    @classmethod
+    def from_dict(cls, d: Mapping[str, Any]) -> "MunisunConfig":
+        return _wrap(_call("config.parse", config=dict(d)))
+
+    def to_dict(self) -> Dict[str, Any]:
+        return dict(self._json)
+
+    def to_model_spec(self) -> ModelSpec:
+        return ModelSpec.from_json(self._spec)
+
+    def __hash__(self) -> int:
+        return hash(json.dumps(self.to_dict(), sort_keys=True))
+
+
 def _wrap(r: Mapping[str, Any]):
     c = r["config"]
+    if r["architecture"] == "Munisun":
+        return MunisunConfig(
+            vocab=c["vocab"], width=c["width"], norm_eps=c["norm"]["eps"],
+            embedding_scale=c["embedding"]["scale"], side_dim=(c.get("token_side") or {}).get("dim", 0),
+            layers=tuple(c["layers"]), eos_token_ids=tuple(r["eos_token_ids"]), _json=c, _spec=r["spec"])
     if r["architecture"] == "Kefesun":
         return KefesunConfig(
             vocab=c["vocab"], width=c["width"], norm_eps=c["norm"]["eps"],
@@ -360,4 +400,4 @@ def config_from_dir(model_dir: str):
 
 
 __all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config",
-           "ZuzelornConfig", "DunavikConfig", "KefesunConfig", "config_from_dict", "config_from_dir", "known_architectures"]
+           "ZuzelornConfig", "DunavikConfig", "KefesunConfig", "MunisunConfig", "config_from_dict", "config_from_dir", "known_architectures"]

@@ -37,6 +37,7 @@ static Tables &ready() {
         register_zuzelorn();
         register_dunavik();
         register_kefesun();
+        register_munisun();
     });
     return raw_tables();
 }

@@ -37,10 +37,11 @@ std::string architecture_name(const Json &config_json);
 std::unique_ptr<ArchConfig> config_from_json(const Json &config_json);
 std::unique_ptr<ArchConfig> config_from_dir(const std::string &model_dir);
 
-// defined in qwen3.cpp, zuzelorn.cpp, dunavik.cpp and kefesun.cpp; called once by the registry
+// defined in qwen3.cpp, zuzelorn.cpp, dunavik.cpp, kefesun.cpp and munisun.cpp; called once by the registry
 void register_qwen3();
 void register_zuzelorn();
 void register_dunavik();
 void register_kefesun();
+void register_munisun();
 
 }  // namespace jb

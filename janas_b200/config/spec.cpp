@@ -112,6 +112,10 @@ Json ModelSpec::to_json() const {
     if (!position_table_name.empty()) j.set("position_table_name", position_table_name);
     if (logit_scale != 1.0) j.set("logit_scale", logit_scale);
     if (embedding_scale != 1.0) j.set("embedding_scale", embedding_scale);
+    if (!token_table_name.empty()) {
+        j.set("token_table_name", token_table_name);
+        j.set("token_table_width", token_table_width);
+    }
     j.set("embedding_name", embedding_name);
     j.set("final_norm_name", final_norm_name);
     j.set("head_name", head_name);
@@ -168,6 +172,8 @@ ModelSpec ModelSpec::from_json(const Json &j) {
     s.position_table_name = str_or(j, "position_table_name", "");
     if (j.get("logit_scale").is_number()) s.logit_scale = j.get("logit_scale").as_double();
     if (j.get("embedding_scale").is_number()) s.embedding_scale = j.get("embedding_scale").as_double();
+    s.token_table_name = str_or(j, "token_table_name", "");
+    if (j.get("token_table_width").is_number()) s.token_table_width = j.get("token_table_width").as_int();
     s.embedding_name = str_or(j, "embedding_name", s.embedding_name);
     s.final_norm_name = str_or(j, "final_norm_name", s.final_norm_name);
     s.head_name = str_or(j, "head_name", s.head_name);

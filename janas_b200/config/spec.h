@@ -100,6 +100,10 @@ struct ModelSpec {
     // a factor on the embedding rows as they enter the residual stream (a tied head reads
     // the table without it)
     double embedding_scale = 1.0;
+    // a second table [vocab, token_table_width] of vectors per token ("" for none), which
+    // the layers' blocks read by columns (a per-layer input of the token itself)
+    std::string token_table_name;
+    long long token_table_width = 0;
     std::string embedding_name = "model.embed_tokens.weight";
     std::string final_norm_name = "model.norm";
     std::string head_name = "lm_head.weight";

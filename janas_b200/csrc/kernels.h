@@ -24,6 +24,11 @@
 #define JB_ACT_RELU2 0
 #define JB_ACT_RELU 1
 #define JB_ACT_GELU_TANH 2
+#define JB_ACT_SILU 3
+// modes of jb_qkv_prepare_append: the rotation turns neighbours (2i, 2i + 1) instead of (i, i + half);
+// q and k heads are divided by their root mean square after the rotation
+#define JB_ROT_PAIRS 1
+#define JB_UNIT_NORM 2
 
 #ifdef __cplusplus
 extern "C" {
@@ -136,7 +141,7 @@ int jb_qkv_prepare_append(const float *qkv, int S, long long split_stride, int l
                           const float *sn, int rot_half, const int32_t *row_pos,
                           const int32_t *row_seq, const int32_t *block_table, int bt_stride,
                           void *q_out, void *k_cache, void *v_cache, int cache_dt, int n, int nh,
-                          int nkv, int hd, int vd, cudaStream_t st);
+                          int nkv, int hd, int vd, int mode, cudaStream_t st);
 int jb_norm_residual(float *x, const float *a, int Sa, long long a_stride, const float *a_bias,
                      const void *skip, int skip_dt, const float *coef, int coef_ld, const float *w,
                      const float *bias, int n, int dm, float eps, int rms, int few_rows,
@@ -152,7 +157,29 @@ int jb_mingru(const float *P, int S, long long stride, int ld, int col0, const f
               cudaStream_t st);
 int jb_moe_route(const float *P, int S, long long stride, int ld, int col0, const float *correction,
                  float *weights, float *skip_coef, int n, int E, int groups, int keep, int top,
-                 int first_identity, float scale, cudaStream_t st);
+                 int first_identity, float scale, int sigmoid_scores, int group_best, cudaStream_t st);
+int jb_gated_weighted(const float *z, int S, long long stride, int ld, const float *weights, int w_ld,
+                      int n_experts, int ff, int kind, void *out, int out_dt, int n, cudaStream_t st);
+int jb_causal_conv(const float *u, int S, long long stride, int ld, int col0, const float *w,
+                   const float *bias, float *state, long long slot_stride, const int32_t *row_pos,
+                   const int32_t *row_seq, const int32_t *seq_slot, void *out, int out_dt, int out_ld,
+                   int n, int C, int taps, int act, int what, cudaStream_t st);
+int jb_matrix_state_scan(const float *src, int S, long long stride, int ld, int val_col0, int key_col0,
+                         int qry_col0, int silu, const float *dt, int dt_S, long long dt_stride,
+                         int dt_ld, int dt_col0, const float *dt_bias, const float *a_log,
+                         const float *skip, const float *decay, float *state, long long slot_stride,
+                         const int32_t *row_seq, const int32_t *seq_slot, float *y, int n, int n_seqs,
+                         int H, int G, int N, int P, int every_row_starts, cudaStream_t st);
+int jb_gated_part_norm(const float *y, const float *pre, int pre_S, long long pre_stride, int pre_ld,
+                       int pre_col0, const float *post, int post_S, long long post_stride, int post_ld,
+                       int post_col0, const float *w, float eps, void *out, int out_dt, int n, int width,
+                       int parts, cudaStream_t st);
+int jb_pair_combine(const float *L, int SL, long long strideL, const float *R, int SR, long long strideR,
+                    const float *wl, const float *wr, float sl, float sr, float eps, float *out, int n,
+                    int m, cudaStream_t st);
+int jb_token_gate(const float *P, int S, long long stride, int ld, const void *table, int table_dt,
+                  int table_ld, int col0, const int32_t *tokens, void *out, int out_dt, int n, int dim,
+                  cudaStream_t st);
 int jb_activation_weighted(const float *z, int S, long long stride, int ld, const float *weights,
                            int w_ld, int n_experts, int ff, int kind, void *out, int out_dt, int n,
                            int width, cudaStream_t st);

@@ -210,8 +210,90 @@ Buf moe_route(Device &d, const Stack &P, long long col0, const RouteParams &r, B
     if (skip_coef) *skip_coef = d.pool.get(std::max<size_t>((size_t)P.n * 4, 16));
     check(jb_moe_route(P.data(), P.S, P.stride(), as_int(P.m, "width"), (int)col0, r.correction,
                        weights.as<float>(), skip_coef ? skip_coef->as<float>() : nullptr, as_int(P.n, "rows"),
-                       r.experts, r.groups, r.keep, r.top, r.first_identity, r.scale, d.stream), "moe_route");
+                       r.experts, r.groups, r.keep, r.top, r.first_identity, r.scale, r.sigmoid_scores ? 1 : 0,
+                       r.group_best, d.stream), "moe_route");
     return weights;
+}
+
+Buf gated_weighted(Device &d, const Stack &z, const float *weights, int w_ld, int n_experts, long long ff,
+                   int kind, DType out_dt) {
+    need_float(out_dt, "activation output");
+    long long width = (long long)n_experts * ff;
+    if (width <= 0 || 2 * width > z.m) fail(JB_LLM_EINVAL, "gated_weighted: the product is narrower than the experts");
+    Buf out = d.pool.get((size_t)z.n * (size_t)width * dtype_size(out_dt));
+    check(jb_gated_weighted(z.data(), z.S, z.stride(), as_int(z.m, "width"), weights, w_ld, n_experts,
+                            as_int(ff, "width"), kind, out.ptr, out_dt, as_int(z.n, "rows"), d.stream),
+          "gated_weighted");
+    return out;
+}
+
+Buf causal_conv(Device &d, const Stack &u, long long col0, long long C, const float *w, const float *bias,
+                int taps, float *state, long long slot_stride, const int32_t *row_pos, const int32_t *row_seq,
+                const int32_t *seq_slot, bool silu, DType out_dt, bool write_out, bool write_state) {
+    need_float(out_dt, "causal_conv output");
+    if (!u || col0 < 0 || C <= 0 || col0 + C > u.m) fail(JB_LLM_EINVAL, "causal_conv: the columns lie outside the product");
+    Buf out;
+    if (write_out) out = d.pool.get((size_t)u.n * (size_t)C * dtype_size(out_dt));
+    int what = (write_out ? 1 : 0) | (write_state && taps > 1 ? 2 : 0);
+    if (!what) return out;
+    check(jb_causal_conv(u.data(), u.S, u.stride(), as_int(u.m, "width"), (int)col0, w, bias, state, slot_stride,
+                         row_pos, row_seq, seq_slot, out.ptr, out_dt, as_int(C, "width"), as_int(u.n, "rows"),
+                         as_int(C, "width"), taps, silu ? 1 : 0, what, d.stream), "causal_conv");
+    return out;
+}
+
+Buf matrix_state_scan(Device &d, const Stack &src, const MatrixScan &m, float *state, long long slot_stride,
+                      const int32_t *row_seq, const int32_t *seq_slot, int n_seqs, bool every_row_starts) {
+    if (!src || !state) fail(JB_LLM_EINVAL, "matrix_state_scan: no input or no state");
+    if (m.dt && m.dt->n != src.n) fail(JB_LLM_EINVAL, "matrix_state_scan: the steps are of other rows");
+    Buf y = d.pool.get(std::max<size_t>((size_t)src.n * (size_t)m.H * (size_t)m.P * 4, 16));
+    check(jb_matrix_state_scan(src.data(), src.S, src.stride(), as_int(src.m, "width"), (int)m.val_col0,
+                               (int)m.key_col0, (int)m.qry_col0, m.silu ? 1 : 0, m.dt ? m.dt->data() : nullptr,
+                               m.dt ? m.dt->S : 0, m.dt ? m.dt->stride() : 0, m.dt ? as_int(m.dt->m, "width") : 0,
+                               (int)m.dt_col0, m.dt_bias, m.a_log, m.skip, m.decay, state, slot_stride, row_seq,
+                               seq_slot, y.as<float>(), as_int(src.n, "rows"), n_seqs, m.H, m.G, m.N, m.P,
+                               every_row_starts ? 1 : 0, d.stream), "matrix_state_scan");
+    return y;
+}
+
+Buf gated_part_norm(Device &d, const float *y, long long n, long long width, int parts, const Stack *pre,
+                    long long pre_col0, const Stack *post, long long post_col0, const float *w, float eps,
+                    DType out_dt) {
+    need_float(out_dt, "gated_part_norm output");
+    if ((pre && pre->n != n) || (post && post->n != n)) fail(JB_LLM_EINVAL, "gated_part_norm: a gate of other rows");
+    Buf out = d.pool.get(std::max<size_t>((size_t)n * (size_t)width * dtype_size(out_dt), 16));
+    check(jb_gated_part_norm(y, pre ? pre->data() : nullptr, pre ? pre->S : 0, pre ? pre->stride() : 0,
+                             pre ? as_int(pre->m, "width") : 0, (int)pre_col0, post ? post->data() : nullptr,
+                             post ? post->S : 0, post ? post->stride() : 0, post ? as_int(post->m, "width") : 0,
+                             (int)post_col0, w, eps, out.ptr, out_dt, as_int(n, "rows"), as_int(width, "width"),
+                             parts, d.stream), "gated_part_norm");
+    return out;
+}
+
+Stack pair_combine(Device &d, const Stack &L, const Stack &R, const float *wl, const float *wr, float sl,
+                   float sr, float eps) {
+    if (!L || !R || L.n != R.n || L.m != R.m) fail(JB_LLM_EINVAL, "pair_combine: the two results differ in shape");
+    if (L.bias || R.bias || L.skip || R.skip) fail(JB_LLM_EINVAL, "pair_combine: a result still has a term to be added");
+    Stack out;
+    out.S = 1;
+    out.n = L.n;
+    out.m = L.m;
+    out.buf = d.pool.get(std::max<size_t>((size_t)L.n * (size_t)L.m * 4, 16));
+    check(jb_pair_combine(L.data(), L.S, L.stride(), R.data(), R.S, R.stride(), wl, wr, sl, sr, eps, out.data(),
+                          as_int(L.n, "rows"), as_int(L.m, "width"), d.stream), "pair_combine");
+    return out;
+}
+
+Buf token_gate(Device &d, const Stack &P, const DevTensor &table, long long col0, long long dim,
+               const int32_t *tokens, DType out_dt) {
+    need_float(out_dt, "token_gate output");
+    if (!P || P.m < dim || table.shape.size() != 2 || col0 < 0 || col0 + dim > table.shape[1])
+        fail(JB_LLM_EINVAL, "token_gate: the columns lie outside the table or the product");
+    Buf out = d.pool.get(std::max<size_t>((size_t)P.n * (size_t)dim * dtype_size(out_dt), 16));
+    check(jb_token_gate(P.data(), P.S, P.stride(), as_int(P.m, "width"), table.ptr, table.dt,
+                        as_int(table.shape[1], "width"), (int)col0, tokens, out.ptr, out_dt, as_int(P.n, "rows"),
+                        as_int(dim, "width"), d.stream), "token_gate");
+    return out;
 }
 
 Buf activation_weighted(Device &d, const Stack &z, long long width, const float *weights, int w_ld, int n_experts,
@@ -227,7 +309,8 @@ Buf activation_weighted(Device &d, const Stack &z, long long width, const float 
 
 Buf qkv_prepare_append(Device &d, const Stack &qkv, const float *bias, const float *q_w, const float *k_w,
                        float eps, const float *cos, const float *sin, int rot_half, const int32_t *row_pos,
-                       const int32_t *row_seq, const AttnCache &c, const AttnGeometry &g, DType out_dt) {
+                       const int32_t *row_seq, const AttnCache &c, const AttnGeometry &g, DType out_dt,
+                       bool pairs, bool unit_norm) {
     bool append = c.writes;
     long long width = (long long)g.nh * g.hd + (append ? (long long)g.nkv * (g.hd + g.value_dim()) : 0);
     if (qkv.m < width) fail(JB_LLM_EINVAL, "qkv_prepare_append: the product is narrower than q, k and v");
@@ -237,7 +320,9 @@ Buf qkv_prepare_append(Device &d, const Stack &qkv, const float *bias, const flo
     check(jb_qkv_prepare_append(qkv.data(), qkv.S, qkv.stride(), as_int(qkv.m, "width"), bias, q_w, k_w, eps, cos,
                                 sin, rot_half, row_pos, row_seq, c.block_table, c.bt_stride, q.ptr,
                                 append ? c.k : nullptr, append ? c.v : nullptr, out_dt, as_int(qkv.n, "rows"),
-                                g.nh, g.nkv, g.hd, g.value_dim(), d.stream), "qkv_prepare_append");
+                                g.nh, g.nkv, g.hd, g.value_dim(),
+                                (pairs ? JB_ROT_PAIRS : 0) | (unit_norm ? JB_UNIT_NORM : 0), d.stream),
+          "qkv_prepare_append");
     return q;
 }
 
@@ -247,6 +332,7 @@ int activation_kind(const std::string &name) {
     if (name == "relu2") return JB_ACT_RELU2;
     if (name == "relu") return JB_ACT_RELU;
     if (name == "gelu_tanh") return JB_ACT_GELU_TANH;
+    if (name == "silu") return JB_ACT_SILU;
     return -1;
 }
 

@@ -121,12 +121,55 @@ struct RouteParams {
     int experts = 0, groups = 1, keep = 1, top = 1, first_identity = 0;
     float scale = 1.0f;
     const float *correction = nullptr;
+    bool sigmoid_scores = false;      // each score the sigmoid of its logit, instead of a softmax over all
+    int group_best = 1;               // a group's score: the sum of this many of its largest choices
 };
 Buf moe_route(Device &d, const Stack &P, long long col0, const RouteParams &r, Buf *skip_coef);
 // act(sum z) * weights[row, column / ff] over the first n_experts * ff columns of z, act
 // alone over the rest up to width: [n, width] in out_dt.  weights: float32 [n, w_ld].
 Buf activation_weighted(Device &d, const Stack &z, long long width, const float *weights, int w_ld, int n_experts,
                         long long ff, int kind, DType out_dt);
+
+// The same for experts with a gate: per expert [gate (ff) | up (ff)] in z's columns;
+// act(gate) * up * weights[row, expert] as [n, n_experts ff] in out_dt.
+Buf gated_weighted(Device &d, const Stack &z, const float *weights, int w_ld, int n_experts, long long ff,
+                   int kind, DType out_dt);
+
+// A causal convolution over time on C columns (from col0) of a product's sums u, without
+// the input added: act(bias + sum_j w[:, j] u_{t - taps + 1 + j}) as [n, C] in out_dt (act:
+// "" or "silu"; bias float32 [C] or null; w float32 [C, taps]).  state: float32
+// [taps - 1, C] per slot, slot_stride floats apart.  write_out / write_state as short_conv.
+Buf causal_conv(Device &d, const Stack &u, long long col0, long long C, const float *w, const float *bias,
+                int taps, float *state, long long slot_stride, const int32_t *row_pos, const int32_t *row_seq,
+                const int32_t *seq_slot, bool silu, DType out_dt, bool write_out, bool write_state);
+
+// A recurrence with a matrix of N x P values per head as state (csrc/matrix_state.cu):
+// S_t = a_t S_{t-1} + b_t k_t v_t^T, y_t = S_t^T q_t + d v_t; y comes back as float32 [n, H P].
+// src holds v (H P columns from val_col0), k and q (G N columns each).  With dt (the steps'
+// sums, H columns from dt_col0): a = exp(-exp(a_log) softplus(dt + dt_bias)), b = that
+// softplus, d = skip; without: a = decay[h], b = 1, d = 0.  silu: v, k, q are silu(sum).
+// state: float32 [H, N, P] per slot, slot_stride floats apart.
+struct MatrixScan {
+    int H = 0, G = 0, N = 0, P = 0;
+    long long val_col0 = 0, key_col0 = 0, qry_col0 = 0, dt_col0 = 0;
+    bool silu = false;
+    const Stack *dt = nullptr;
+    const float *dt_bias = nullptr, *a_log = nullptr, *skip = nullptr, *decay = nullptr;
+};
+Buf matrix_state_scan(Device &d, const Stack &src, const MatrixScan &m, float *state, long long slot_stride,
+                      const int32_t *row_seq, const int32_t *seq_slot, int n_seqs, bool every_row_starts);
+// rms(y * silu(pre)) in `parts` equal parts of the row, times w, times sigmoid(post): y float32
+// [n, width]; pre / post: sums whose columns from pre_col0 / post_col0 are read (null: none).
+Buf gated_part_norm(Device &d, const float *y, long long n, long long width, int parts, const Stack *pre,
+                    long long pre_col0, const Stack *post, long long post_col0, const float *w, float eps,
+                    DType out_dt);
+// Two results as one stack of one sum: sl * sum(L) + sr * sum(R), or with weights (float32
+// [m] each) sl * rms(sum L) wl + sr * rms(sum R) wr.
+Stack pair_combine(Device &d, const Stack &L, const Stack &R, const float *wl, const float *wr, float sl,
+                   float sr, float eps);
+// gelu_tanh(sum P) * table[tokens[row], col0 .. col0 + dim - 1] as [n, dim] in out_dt
+Buf token_gate(Device &d, const Stack &P, const DevTensor &table, long long col0, long long dim,
+               const int32_t *tokens, DType out_dt);
 
 // RMSNorm of the rows of x (float32 [n, dm]).  With delta, x is first updated in
 // place, x += delta[0] + ... + delta[S-1].  With rows (n_out int32 indices on the
@@ -239,9 +282,13 @@ DevTensor transpose_heads(Device &d, const DevTensor &w, int H);
 // q, k, v out of the fused product's sums (bias: float32 over its columns or null): per-head
 // RMS norm of q and k (weights float32 [hd], or null), rotation of the first 2 rot_half
 // values of a head, K and V (of their own head size) into the cache.  Returns q [n, heads, hd].
+// pairs: the rotation turns neighbours (2i, 2i + 1) by angle i instead of (i, i + rot_half);
+// unit_norm: q and k heads are divided by their root mean square (eps inside the root)
+// after the rotation, without a weight.
 Buf qkv_prepare_append(Device &d, const Stack &qkv, const float *bias, const float *q_w, const float *k_w,
                        float eps, const float *cos, const float *sin, int rot_half, const int32_t *row_pos,
-                       const int32_t *row_seq, const AttnCache &c, const AttnGeometry &g, DType out_dt);
+                       const int32_t *row_seq, const AttnCache &c, const AttnGeometry &g, DType out_dt,
+                       bool pairs = false, bool unit_norm = false);
 // chunks that the kept first tokens of a windowed mixer add to a row's range
 int attention_kept_chunks(int window, int keep_first);
 

@@ -33,6 +33,8 @@ __device__ __forceinline__ void warp_argmax(float &v, int &i)
 //   the E experts form `groups` equal groups of neighbours; a group's score is its largest
 //   choice; only the `keep` best groups' experts can be chosen; the `top` largest choices
 //   among them are chosen (the lower index wins a tie); weight_e = s_e * scale.
+// With sigmoid_scores, s = sigmoid(logits), each on its own, instead of the softmax; with
+// group_best = b > 1 a group's score is the sum of its b largest choices.
 // weights: [n, E], the weight of every chosen expert and 0 for the others.  skip_coef
 // [n]: the sum of the weights of the chosen experts from first_identity on (experts whose
 // output is their input).  Shared memory: 2 E + groups floats per warp.
@@ -40,7 +42,7 @@ __global__ void __launch_bounds__(128)
 moe_route_kernel(const float *__restrict__ P, int S, size_t stride, int ld, int col0,
                  const float *__restrict__ correction, float *__restrict__ weights,
                  float *__restrict__ skip_coef, int n, int E, int groups, int keep, int top,
-                 int first_identity, float scale)
+                 int first_identity, float scale, int sigmoid_scores, int group_best)
 {
     extern __shared__ float sm[];
     pdl_trigger();
@@ -58,10 +60,10 @@ moe_route_kernel(const float *__restrict__ P, int S, size_t stride, int ld, int 
     mx = warp_max(mx);
     float sum = 0.0f;
     for (int e = lane; e < E; e += 32) {
-        s[e] = expf(s[e] - mx);
+        s[e] = sigmoid_scores ? 1.0f / (1.0f + expf(-s[e])) : expf(s[e] - mx);
         sum += s[e];
     }
-    sum = warp_sum(sum);
+    sum = sigmoid_scores ? 1.0f : warp_sum(sum);
     for (int e = lane; e < E; e += 32) {
         s[e] = s[e] / sum;
         choice[e] = s[e] + (correction != nullptr ? correction[e] : 0.0f);
@@ -71,9 +73,23 @@ moe_route_kernel(const float *__restrict__ P, int S, size_t stride, int ld, int 
     int per = E / groups;
     if (keep < groups) {
         for (int g = lane; g < groups; g += 32) {
-            float m = -INFINITY;
-            for (int e = g * per; e < (g + 1) * per; e++)
-                m = fmaxf(m, choice[e]);
+            // the largest choice of the group, or the sum of its group_best largest
+            float m = 0.0f, last = INFINITY;
+            int last_e = -1;
+            for (int k = 0; k < group_best && k < per; k++) {
+                float b = -INFINITY;
+                int be = -1;
+                for (int e = g * per; e < (g + 1) * per; e++)
+                    if ((choice[e] < last || (choice[e] == last && e > last_e)) && choice[e] > b) {
+                        b = choice[e];
+                        be = e;
+                    }
+                if (be < 0)
+                    break;
+                m += b;
+                last = b;
+                last_e = be;
+            }
             gs[g] = m;
         }
         __syncwarp();
@@ -129,6 +145,8 @@ __device__ __forceinline__ float act_value(float v, int kind)
     }
     if (kind == JB_ACT_RELU)
         return fmaxf(v, 0.0f);
+    if (kind == JB_ACT_SILU)
+        return v / (1.0f + expf(-v));
     float u = 0.7978845608028654f * fmaf(0.044715f * v * v, v, v);
     return 0.5f * v * (1.0f + tanhf(u));
 }
@@ -175,6 +193,30 @@ activation_weighted_kernel(const float *__restrict__ z, int S, size_t stride, in
     }
 }
 
+// The same for experts with a gate: expert e's sums are [gate (ff) | up (ff)] in columns
+// 2 e ff .. of z, and out[r, e ff + j] = act(gate_j) * up_j * weights[r, e]; out: [n, n_experts ff].
+template <typename TO>
+__global__ void __launch_bounds__(256)
+gated_weighted_kernel(const float *__restrict__ z, int S, size_t stride, int ld,
+                      const float *__restrict__ weights, int w_ld, int ff, int kind,
+                      TO *__restrict__ out, int width)
+{
+    pdl_trigger();
+    int r = blockIdx.x, c = (int)(blockIdx.y * blockDim.x + threadIdx.x);
+    if (c >= width)
+        return;
+    pdl_wait();
+    int e = c / ff, j = c - e * ff;
+    float wgt = weights[(size_t)r * w_ld + e];
+    float v = 0.0f;
+    if (wgt != 0.0f) {
+        const float *src = z + (size_t)r * ld + (size_t)2 * e * ff + j;
+        float g = add_partials(0.0f, src, S, stride), u = add_partials(0.0f, src + ff, S, stride);
+        v = act_value(g, kind) * u * wgt;
+    }
+    out[(size_t)r * width + c] = from_f<TO>(v);
+}
+
 // y[r, c] += coef[r * coef_ld] * skip[r, c]: a part's own input handed on with a weight
 // per row (what identity experts give), for consumers that do not take it themselves.
 template <typename TS>
@@ -215,16 +257,16 @@ extern "C" int jb_add_row_scaled(float *y, const void *skip, int skip_dt, const 
 extern "C" int jb_moe_route(const float *P, int S, long long stride, int ld, int col0,
                             const float *correction, float *weights, float *skip_coef, int n, int E,
                             int groups, int keep, int top, int first_identity, float scale,
-                            cudaStream_t st)
+                            int sigmoid_scores, int group_best, cudaStream_t st)
 {
     if (n <= 0)
         return JB_OK;
     if (E <= 0 || E > 2048 || groups <= 0 || E % groups || keep <= 0 || keep > groups || top <= 0 || top > E ||
-        ld < col0 + E || S <= 0 || first_identity < 0)
+        ld < col0 + E || S <= 0 || first_identity < 0 || group_best < 1)
         return JB_EINVAL;
     size_t smem = (size_t)4 * (2 * E + groups) * 4;
     launch(moe_route_kernel, (unsigned)((n + 3) / 4), 128, smem, st, P, S, (size_t)stride, ld, col0, correction,
-           weights, skip_coef, n, E, groups, keep, top, first_identity, scale);
+           weights, skip_coef, n, E, groups, keep, top, first_identity, scale, sigmoid_scores, group_best);
     return launch_status();
 }
 
@@ -240,7 +282,7 @@ extern "C" int jb_activation_weighted(const float *z, int S, long long stride, i
         ff = 4;          // no weighted columns: the blocks' size only has to divide a thread's values
     if (width <= 0 || ld < width || ff <= 0 || n_experts < 0 || (long long)n_experts * ff > width ||
         (n_experts > 0 && (weights == nullptr || w_ld < n_experts)) || S <= 0 ||
-        (kind != JB_ACT_RELU2 && kind != JB_ACT_RELU && kind != JB_ACT_GELU_TANH))
+        (kind != JB_ACT_RELU2 && kind != JB_ACT_RELU && kind != JB_ACT_GELU_TANH && kind != JB_ACT_SILU))
         return JB_EINVAL;
     bool vec = ff % 4 == 0 && width % 4 == 0 && ld % 4 == 0 && stride % 4 == 0 && (uintptr_t)z % 16 == 0 &&
                (uintptr_t)out % 16 == 0;
@@ -259,5 +301,29 @@ extern "C" int jb_activation_weighted(const float *z, int S, long long stride, i
         return JB_EINVAL;
     }
 #undef JB_AW
+    return launch_status();
+}
+
+// z: float32 [S, n, ld] whose first 2 n_experts ff columns are, per expert, ff gate values and
+// then ff up values; weights: float32 [n, w_ld].  out: [n, n_experts ff] in out_dt.
+extern "C" int jb_gated_weighted(const float *z, int S, long long stride, int ld, const float *weights, int w_ld,
+                                 int n_experts, int ff, int kind, void *out, int out_dt, int n, cudaStream_t st)
+{
+    if (n <= 0)
+        return JB_OK;
+    long long width = (long long)n_experts * ff;
+    if (n_experts <= 0 || ff <= 0 || ld < 2 * width || width > 0x7fffffffll || weights == nullptr || w_ld < n_experts ||
+        S <= 0 || (kind != JB_ACT_RELU2 && kind != JB_ACT_RELU && kind != JB_ACT_GELU_TANH && kind != JB_ACT_SILU) ||
+        (width + 255) / 256 > 65535)
+        return JB_EINVAL;
+    dim3 grid((unsigned)n, (unsigned)((width + 255) / 256));
+    if (out_dt == JB_F32)
+        launch(gated_weighted_kernel<float>, grid, 256, 0, st, z, S, (size_t)stride, ld, weights, w_ld, ff, kind,
+               (float *)out, (int)width);
+    else if (out_dt == JB_BF16)
+        launch(gated_weighted_kernel<bf16>, grid, 256, 0, st, z, S, (size_t)stride, ld, weights, w_ld, ff, kind,
+               (bf16 *)out, (int)width);
+    else
+        return JB_EINVAL;
     return launch_status();
 }

@@ -509,10 +509,13 @@ def mingru(P: torch.Tensor, width: int, bias: Optional[torch.Tensor], state: tor
 
 
 def moe_route(P: torch.Tensor, col0: int, outputs: int, correction: Optional[torch.Tensor], groups: int,
-              keep: int, top: int, first_identity: int, scale: float) -> Tuple[torch.Tensor, torch.Tensor]:
+              keep: int, top: int, first_identity: int, scale: float, sigmoid_scores: bool = False,
+              group_best: int = 1) -> Tuple[torch.Tensor, torch.Tensor]:
     """The router of a routed feed-forward over the logits in columns col0 .. col0 + outputs - 1
     of the sums P [S, n, ld]: (weights [n, outputs], 0 for outputs not chosen; the summed
-    weight of the chosen outputs from first_identity on, [n])."""
+    weight of the chosen outputs from first_identity on, [n]).  sigmoid_scores: each score is
+    the sigmoid of its logit instead of a softmax over all; group_best: a group's score is the
+    sum of that many of its largest choice scores."""
     P = stack(P)
     _need(P, "P", torch.float32, (None, None, None))
     S, n, ld = P.shape
@@ -521,8 +524,117 @@ def moe_route(P: torch.Tensor, col0: int, outputs: int, correction: Optional[tor
     weights = torch.empty((n, outputs), dtype=torch.float32, device=P.device)
     skip = torch.empty((n,), dtype=torch.float32, device=P.device)
     _check(lib().jb_moe_route(_p(P), S, n * ld, ld, col0, _p(correction), _p(weights), _p(skip), n, outputs,
-                              groups, keep, top, first_identity, float(scale), _stream()), "moe_route")
+                              groups, keep, top, first_identity, float(scale), 1 if sigmoid_scores else 0,
+                              group_best, _stream()), "moe_route")
     return weights, skip
+
+
+def gated_weighted(z: torch.Tensor, weights: torch.Tensor, n_experts: int, ff: int, kind: str,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """act(gate) * up * weights[row, expert] for experts whose sums lie [gate (ff) | up (ff)] one
+    after the other in z [S, n, ld]: [n, n_experts * ff]."""
+    z = stack(z)
+    _need(z, "z", torch.float32, (None, None, None))
+    S, n, ld = z.shape
+    _need(weights, "weights", torch.float32, (n, None))
+    out = torch.empty((n, n_experts * ff), dtype=out_dtype, device=z.device)
+    kinds = {"relu2": 0, "relu": 1, "gelu_tanh": 2, "silu": 3}
+    _check(lib().jb_gated_weighted(_p(z), S, n * ld, ld, _p(weights), weights.shape[1], n_experts, ff,
+                                   kinds[kind], _p(out), _DT[out_dtype], n, _stream()), "gated_weighted")
+    return out
+
+
+def causal_conv(u: torch.Tensor, col0: int, C: int, w: torch.Tensor, bias: Optional[torch.Tensor],
+                state: Optional[torch.Tensor], row_pos: torch.Tensor, row_seq: torch.Tensor,
+                seq_slot: torch.Tensor, silu: bool, out_dtype: torch.dtype, write_out: bool = True,
+                write_state: bool = True, slot_stride: Optional[int] = None) -> Optional[torch.Tensor]:
+    """A causal convolution over time on columns col0 .. col0 + C - 1 of the sums u [S, n, ld],
+    without the input added: act(bias + sum_j w[:, j] u_{t - taps + 1 + j}); w float32 [C, taps];
+    state: float32, per slot a ring [taps - 1, C] of the last inputs (slot_stride floats apart)."""
+    u = stack(u)
+    _need(u, "u", torch.float32, (None, None, None))
+    S, n, ld = u.shape
+    _need(w, "w", torch.float32, (C, None))
+    taps = w.shape[1]
+    out = torch.empty((n, C), dtype=out_dtype, device=u.device) if write_out else None
+    what = (1 if write_out else 0) | (2 if write_state and taps > 1 else 0)
+    stride = slot_stride if slot_stride is not None else (taps - 1) * C
+    _check(lib().jb_causal_conv(_p(u), S, n * ld, ld, col0, _p(w), _p(bias), _p(state), stride, _p(row_pos),
+                                _p(row_seq), _p(seq_slot), _p(out), _DT[out_dtype], C, n, C, taps,
+                                1 if silu else 0, what, _stream()), "causal_conv")
+    return out
+
+
+def matrix_state_scan(src: torch.Tensor, H: int, G: int, N: int, P: int, val_col0: int, key_col0: int,
+                      qry_col0: int, state: torch.Tensor, row_seq: torch.Tensor, seq_slot: torch.Tensor,
+                      n_seqs: int, every_row_starts: bool = False, silu: bool = False,
+                      dt: Optional[torch.Tensor] = None, dt_col0: int = 0,
+                      dt_bias: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None,
+                      skip: Optional[torch.Tensor] = None, decay: Optional[torch.Tensor] = None,
+                      slot_stride: Optional[int] = None) -> torch.Tensor:
+    """S_t = a_t S_{t-1} + b_t k_t v_t^T, y_t = S_t^T q_t + d v_t per head over the rows of each
+    sequence; src [S, n, ld] holds v (H P columns), k and q (G N columns each).  With dt (sums
+    with H columns from dt_col0): a = exp(-exp(a_log) softplus(dt + dt_bias)), b = the softplus,
+    d = skip; otherwise a = decay, b = 1, d = 0.  state: float32 [slots, H, N, P].  y: [n, H P]."""
+    src = stack(src)
+    _need(src, "src", torch.float32, (None, None, None))
+    S, n, ld = src.shape
+    dS = dn = dld = 0
+    if dt is not None:
+        dt = stack(dt)
+        _need(dt, "dt", torch.float32, (None, n, None))
+        dS, dn, dld = dt.shape
+    y = torch.empty((n, H * P), dtype=torch.float32, device=src.device)
+    stride = slot_stride if slot_stride is not None else H * N * P
+    _check(lib().jb_matrix_state_scan(_p(src), S, n * ld, ld, val_col0, key_col0, qry_col0, 1 if silu else 0,
+                                      _p(dt), dS, dn * dld, dld, dt_col0, _p(dt_bias), _p(a_log), _p(skip),
+                                      _p(decay), _p(state), stride, _p(row_seq), _p(seq_slot), _p(y), n, n_seqs,
+                                      H, G, N, P, 1 if every_row_starts else 0, _stream()), "matrix_state_scan")
+    return y
+
+
+def gated_part_norm(y: torch.Tensor, parts: int, w: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                    pre: Optional[torch.Tensor] = None, pre_col0: int = 0,
+                    post: Optional[torch.Tensor] = None, post_col0: int = 0) -> torch.Tensor:
+    """rms(y * silu(pre)) in ``parts`` equal parts of each row, times w, times sigmoid(post)."""
+    _need(y, "y", torch.float32, (None, None))
+    n, width = y.shape
+    _need(w, "w", torch.float32, (width,))
+    pre = None if pre is None else stack(pre)
+    post = None if post is None else stack(post)
+    out = torch.empty((n, width), dtype=out_dtype, device=y.device)
+    a = (0, 0, 0) if pre is None else (pre.shape[0], n * pre.shape[2], pre.shape[2])
+    b = (0, 0, 0) if post is None else (post.shape[0], n * post.shape[2], post.shape[2])
+    _check(lib().jb_gated_part_norm(_p(y), _p(pre), a[0], a[1], a[2], pre_col0, _p(post), b[0], b[1], b[2],
+                                    post_col0, _p(w), float(eps), _p(out), _DT[out_dtype], n, width, parts,
+                                    _stream()), "gated_part_norm")
+    return out
+
+
+def pair_combine(L: torch.Tensor, R: torch.Tensor, wl: Optional[torch.Tensor], wr: Optional[torch.Tensor],
+                 sl: float, sr: float, eps: float) -> torch.Tensor:
+    """sl * sum(L) + sr * sum(R), or with weights sl * rms(sum L) wl + sr * rms(sum R) wr."""
+    L, R = stack(L), stack(R)
+    _need(L, "L", torch.float32, (None, None, None))
+    _need(R, "R", torch.float32, (None, L.shape[1], L.shape[2]))
+    n, m = L.shape[1], L.shape[2]
+    out = torch.empty((n, m), dtype=torch.float32, device=L.device)
+    _check(lib().jb_pair_combine(_p(L), L.shape[0], n * m, _p(R), R.shape[0], n * m, _p(wl), _p(wr), float(sl),
+                                 float(sr), float(eps), _p(out), n, m, _stream()), "pair_combine")
+    return out
+
+
+def token_gate(P: torch.Tensor, table: torch.Tensor, col0: int, dim: int, tokens: torch.Tensor,
+               out_dtype: torch.dtype) -> torch.Tensor:
+    """gelu_tanh(sum P) * table[tokens[row], col0 .. col0 + dim - 1] as [n, dim]."""
+    P = stack(P)
+    _need(P, "P", torch.float32, (None, None, None))
+    S, n, ld = P.shape
+    _need(table, "table", _FLOATS, (None, None))
+    out = torch.empty((n, dim), dtype=out_dtype, device=P.device)
+    _check(lib().jb_token_gate(_p(P), S, n * ld, ld, _p(table), _DT[table.dtype], table.shape[1], col0,
+                               _p(tokens), _p(out), _DT[out_dtype], n, dim, _stream()), "token_gate")
+    return out
 
 
 def activation_weighted(z: torch.Tensor, width: int, weights: torch.Tensor, n_experts: int, ff: int,
@@ -544,8 +656,10 @@ def qkv_prepare_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_weight
                        k_weight: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
                        sin: Optional[torch.Tensor], row_pos: torch.Tensor, row_seq: torch.Tensor,
                        block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                       num_heads: int) -> torch.Tensor:
-    """q, k, v out of the sums of one product [S, n, ld] = [q | k | v | ...]: the bias, an RMS
+                       num_heads: int, pairs: bool = False, unit_norm: bool = False) -> torch.Tensor:
+    """pairs: the rotation turns neighbours (2i, 2i + 1); unit_norm: q and k heads are divided by
+    their root mean square after the rotation.
+    q, k, v out of the sums of one product [S, n, ld] = [q | k | v | ...]: the bias, an RMS
     norm per head on q and k (weights float32 [hd] or None), a rotation of the first
     2 * cos.shape[1] values of each head (value i with value i + cos.shape[1]), K and V
     into the cache pages at the rows' positions.  Returns q [n, heads, hd] in the cache's type."""
@@ -565,7 +679,8 @@ def qkv_prepare_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_weight
                                        float(eps), _p(cos), _p(sin), rot_half, _p(row_pos), _p(row_seq),
                                        _p(block_table), block_table.shape[1], _p(q), _p(k_cache),
                                        _p(v_cache), _DT[k_cache.dtype], n, num_heads, nkv, hd, vd,
-                                       _stream()), "qkv_prepare_append")
+                                       (1 if pairs else 0) | (2 if unit_norm else 0), _stream()),
+           "qkv_prepare_append")
     return q
 
 

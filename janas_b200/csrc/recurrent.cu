@@ -157,6 +157,50 @@ short_conv_rows_kernel(const float *__restrict__ x, const float *__restrict__ w,
     }
 }
 
+// A causal convolution over time on C columns of a product's sums, without the input
+// added:  out[r, c] = act(bias[c] + sum_{j < taps} w[c, j] * u_{t - taps + 1 + j}[c]),
+// u = the sums in columns col0 .. col0 + C - 1 of [S, n, ld]; zeros before position 0.
+// State, `what` and the rule for one launch or two are short_conv_kernel's: a ring of the
+// last taps - 1 inputs per slot, [taps - 1, C].  act 1: silu.  out: [n, out_ld] with the
+// result in its first C columns.  One thread per (row, column).
+template <typename TO>
+__global__ void __launch_bounds__(256)
+causal_conv_kernel(const float *__restrict__ u, int S, size_t stride, int ld, int col0,
+                   const float *__restrict__ w, const float *__restrict__ bias, float *__restrict__ state,
+                   size_t slot_stride, const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
+                   const int32_t *__restrict__ seq_slot, TO *__restrict__ out, int out_ld, int n, int C, int taps,
+                   int act, int what)
+{
+    pdl_trigger();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n * C)
+        return;
+    int r = (int)(idx / C), c = (int)(idx - (size_t)r * C);
+    int pos = row_pos[r], seq = row_seq[r];
+    int keep = taps - 1;
+    float *st = state != nullptr ? state + (size_t)seq_slot[seq] * slot_stride : nullptr;
+    pdl_wait();
+    float cur = add_partials(0.0f, u + (size_t)r * ld + col0 + c, S, stride);
+    if (what & 1) {
+        float acc = bias != nullptr ? bias[c] : 0.0f;
+        acc = fmaf(w[(size_t)c * taps + taps - 1], cur, acc);
+        for (int k = 1; k <= keep; k++) {
+            int p = pos - k;
+            if (p < 0)
+                break;
+            float v = r - k >= 0 && row_seq[r - k] == seq
+                          ? add_partials(0.0f, u + (size_t)(r - k) * ld + col0 + c, S, stride)
+                          : st[(size_t)(p % keep) * C + c];
+            acc = fmaf(w[(size_t)c * taps + taps - 1 - k], v, acc);
+        }
+        if (act == 1)
+            acc = acc / (1.0f + expf(-acc));
+        out[(size_t)r * out_ld + c] = from_f<TO>(acc);
+    }
+    if ((what & 2) && keep > 0 && (r + keep >= n || row_seq[r + keep] != seq))
+        st[(size_t)(pos % keep) * C + c] = cur;
+}
+
 // ---------------------------------------------------------------------- minGRU
 //
 //   z = sigmoid(P_z + b_z);  u = P_x + b_x;  c = u + 1/2 (u >= 0), sigmoid(u) (u < 0)
@@ -416,6 +460,30 @@ extern "C" int jb_short_conv(const float *x, const float *w, float *state, long 
         return JB_EINVAL;
     }
 #undef JB_SC
+    return launch_status();
+}
+
+// u: float32 [S, n, ld]; w: float32 [C, taps]; bias: float32 [C] or null; state: float32
+// [taps - 1, C] per slot (null with taps == 1).  out: [n, out_ld] in out_dt.
+extern "C" int jb_causal_conv(const float *u, int S, long long stride, int ld, int col0, const float *w,
+                              const float *bias, float *state, long long slot_stride, const int32_t *row_pos,
+                              const int32_t *row_seq, const int32_t *seq_slot, void *out, int out_dt, int out_ld,
+                              int n, int C, int taps, int act, int what, cudaStream_t st)
+{
+    if (n <= 0 || C <= 0 || !(what & 3))
+        return JB_OK;
+    if (taps < 1 || S <= 0 || ld < col0 + C || col0 < 0 || out_ld < C || u == nullptr || w == nullptr ||
+        (taps > 1 && state == nullptr) || ((what & 1) && out == nullptr) || (act != 0 && act != 1))
+        return JB_EINVAL;
+    unsigned grid = (unsigned)(((size_t)n * C + 255) / 256);
+    if (out_dt == JB_F32)
+        launch(causal_conv_kernel<float>, grid, 256, 0, st, u, S, (size_t)stride, ld, col0, w, bias, state,
+               (size_t)slot_stride, row_pos, row_seq, seq_slot, (float *)out, out_ld, n, C, taps, act, what);
+    else if (out_dt == JB_BF16)
+        launch(causal_conv_kernel<bf16>, grid, 256, 0, st, u, S, (size_t)stride, ld, col0, w, bias, state,
+               (size_t)slot_stride, row_pos, row_seq, seq_slot, (bf16 *)out, out_ld, n, C, taps, act, what);
+    else
+        return JB_EINVAL;
     return launch_status();
 }
 

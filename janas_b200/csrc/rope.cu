@@ -384,13 +384,14 @@ qkv_prepare_append_kernel(const float *__restrict__ qkv, int S, size_t split_str
                           const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
                           const int32_t *__restrict__ block_table, int bt_stride,
                           TC *__restrict__ q_out, TC *__restrict__ k_cache, TC *__restrict__ v_cache,
-                          int n, int nh, int nkv, int hd, int vd)
+                          int n, int nh, int nkv, int hd, int vd, int mode)
 {
     pdl_trigger();
     unsigned slots = nh + 2 * nkv;
     unsigned task = blockIdx.x * blockDim.y + threadIdx.y;
     if (task >= (unsigned)n * slots)
         return;
+    const bool pairs = mode & JB_ROT_PAIRS, unit = mode & JB_UNIT_NORM;
     unsigned row = task / slots, hs = task - row * slots;
     int lane = threadIdx.x;
     bool is_q = hs < (unsigned)nh;
@@ -425,21 +426,32 @@ qkv_prepare_append_kernel(const float *__restrict__ qkv, int S, size_t split_str
         ss = warp_sum(ss);
     }
     float scale = w != nullptr ? 1.0f / sqrtf(ss / (float)len + eps) : 1.0f;
-    for (int i = lane; i < len; i += 32) {
-        float v = add_partials(b != nullptr ? b[i] : 0.0f, src + i, S, split_stride);
-        if (w != nullptr)
-            v = (v * scale) * w[i];
-        if (i < rot) {
-            int j = i < rot_half ? i + rot_half : i - rot_half;
-            float u = add_partials(b != nullptr ? b[j] : 0.0f, src + j, S, split_stride);
+    // with a norm after the rotation: a pass for the turned values' sum of squares, then the pass that stores
+    float after = 1.0f, ss2 = 0.0f;
+    for (int pass = unit && !is_v ? 0 : 1; pass < 2; pass++) {
+        for (int i = lane; i < len; i += 32) {
+            float v = add_partials(b != nullptr ? b[i] : 0.0f, src + i, S, split_stride);
             if (w != nullptr)
-                u = (u * scale) * w[j];
-            int f = i < rot_half ? i : j;
-            float co = cs[(size_t)pos * rot_half + f], si = sn[(size_t)pos * rot_half + f];
-            // (a, b) -> (a cos - b sin, b cos + a sin), a the lower value of the pair
-            v = i < rot_half ? v * co - u * si : v * co + u * si;
+                v = (v * scale) * w[i];
+            if (i < rot) {
+                // the partner: rot_half values on or back, or the neighbour of the pair (2f, 2f + 1)
+                bool low = pairs ? (i & 1) == 0 : i < rot_half;
+                int j = pairs ? i ^ 1 : low ? i + rot_half : i - rot_half;
+                float u = add_partials(b != nullptr ? b[j] : 0.0f, src + j, S, split_stride);
+                if (w != nullptr)
+                    u = (u * scale) * w[j];
+                int f = pairs ? i >> 1 : low ? i : j;
+                float co = cs[(size_t)pos * rot_half + f], si = sn[(size_t)pos * rot_half + f];
+                // (a, b) -> (a cos - b sin, b cos + a sin), a the lower value of the pair
+                v = low ? v * co - u * si : v * co + u * si;
+            }
+            if (pass == 0)
+                ss2 = fmaf(v, v, ss2);
+            else
+                dst[i] = from_f<TC>(v * after);
         }
-        dst[i] = from_f<TC>(v);
+        if (pass == 0)
+            after = 1.0f / sqrtf(warp_sum(ss2) / (float)len + eps);
     }
 }
 
@@ -457,9 +469,10 @@ qkv_prepare_append_vec_kernel(const float *__restrict__ qkv, int S, size_t split
                               const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
                               const int32_t *__restrict__ block_table, int bt_stride,
                               TC *__restrict__ q_out, TC *__restrict__ k_cache, TC *__restrict__ v_cache,
-                              int n, int nh, int nkv, int hd, int vd)
+                              int n, int nh, int nkv, int hd, int vd, int mode)
 {
     constexpr int PER_WARP = 32 / L;
+    const bool pairs = mode & JB_ROT_PAIRS, unit = mode & JB_UNIT_NORM;
     pdl_trigger();
     unsigned slots = nh + 2 * nkv;
     unsigned total = (unsigned)n * slots;
@@ -483,7 +496,14 @@ qkv_prepare_append_vec_kernel(const float *__restrict__ qkv, int S, size_t split
     float4 wv = make_float4(1.0f, 1.0f, 1.0f, 1.0f), co = wv, si = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (w != nullptr && has)
         wv = load4(w + 4 * l);
-    if (l < 2 * hl) {
+    if (pairs) {
+        // a lane's four values are two pairs: angles 2 l and 2 l + 1 (in co.x, co.y)
+        if (!is_v && 2 * l < rot_half) {
+            const float2 c2 = *reinterpret_cast<const float2 *>(cs + (size_t)pos * rot_half + 2 * l);
+            const float2 s2 = *reinterpret_cast<const float2 *>(sn + (size_t)pos * rot_half + 2 * l);
+            co.x = c2.x; co.y = c2.y; si.x = s2.x; si.y = s2.y;
+        }
+    } else if (l < 2 * hl) {
         int f = 4 * (l < hl ? l : l - hl);
         co = load4(cs + (size_t)pos * rot_half + f);
         si = load4(sn + (size_t)pos * rot_half + f);
@@ -516,7 +536,11 @@ qkv_prepare_append_vec_kernel(const float *__restrict__ qkv, int S, size_t split
         v.x = (v.x * scale) * wv.x; v.y = (v.y * scale) * wv.y;
         v.z = (v.z * scale) * wv.z; v.w = (v.w * scale) * wv.w;
     }
-    if (rot_half > 0) {
+    if (pairs) {
+        if (!is_v && 2 * l < rot_half)
+            v = make_float4(v.x * co.x - v.y * si.x, v.y * co.x + v.x * si.x, v.z * co.y - v.w * si.y,
+                            v.w * co.y + v.z * si.y);
+    } else if (rot_half > 0) {
         int pl = group0 + (l < hl ? l + hl : l < 2 * hl ? l - hl : l);
         float4 u;
         u.x = __shfl_sync(0xffffffffu, v.x, pl);
@@ -530,6 +554,17 @@ qkv_prepare_append_vec_kernel(const float *__restrict__ qkv, int S, size_t split
         else if (l < 2 * hl)
             v = make_float4(v.x * co.x + u.x * si.x, v.y * co.y + u.y * si.y, v.z * co.z + u.z * si.z,
                             v.w * co.w + u.w * si.w);
+    }
+    if (unit) {
+        // a norm without a weight after the rotation, on q and k heads
+        float s2 = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+#pragma unroll
+        for (int o = L / 2; o > 0; o >>= 1)
+            s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+        if (!is_v) {
+            float after = 1.0f / sqrtf(s2 / (float)len + eps);
+            v.x *= after; v.y *= after; v.z *= after; v.w *= after;
+        }
     }
     if (live && has && dst != nullptr)
         store4(dst + 4 * l, v);
@@ -547,12 +582,13 @@ extern "C" int jb_qkv_prepare_append(const float *qkv, int S, long long split_st
                                      const int32_t *row_pos, const int32_t *row_seq,
                                      const int32_t *block_table, int bt_stride, void *q_out,
                                      void *k_cache, void *v_cache, int cache_dt, int n, int nh,
-                                     int nkv, int hd, int vd, cudaStream_t st)
+                                     int nkv, int hd, int vd, int mode, cudaStream_t st)
 {
     if (n <= 0)
         return JB_OK;
     if (hd <= 0 || hd > 512 || vd <= 0 || vd > 512 || rot_half < 0 || 2 * rot_half > hd || nh < 0 || nkv < 0 ||
         (q_w == nullptr) != (k_w == nullptr) || (rot_half > 0 && (cs == nullptr || sn == nullptr)) ||
+        (mode & ~(JB_ROT_PAIRS | JB_UNIT_NORM)) ||
         ld < nh * hd + (k_cache != nullptr ? nkv * (hd + vd) : 0) || (k_cache != nullptr && v_cache == nullptr))
         return JB_EINVAL;
     size_t tasks = (size_t)n * (nh + 2 * nkv);
@@ -561,7 +597,9 @@ extern "C" int jb_qkv_prepare_append(const float *qkv, int S, long long split_st
     dim3 block(32, 4);
     auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
     int big = hd > vd ? hd : vd;
-    if (hd % 4 == 0 && vd % 4 == 0 && rot_half % 4 == 0 && big <= 128 && ld % 4 == 0 && split_stride % 4 == 0 &&
+    // pairs: a lane's two pairs want rot_half even and their angles on an 8-byte boundary
+    bool rot_ok = (mode & JB_ROT_PAIRS) ? rot_half % 2 == 0 : rot_half % 4 == 0;
+    if (hd % 4 == 0 && vd % 4 == 0 && rot_ok && big <= 128 && ld % 4 == 0 && split_stride % 4 == 0 &&
         al16(qkv) && al16(bias) && al16(q_w) && al16(k_w) && al16(cs) && al16(sn) && al16(q_out) &&
         al16(k_cache) && al16(v_cache) && (cache_dt == JB_F32 || cache_dt == JB_BF16) && tasks > 0) {
         int L = big <= 32 ? 8 : big <= 64 ? 16 : 32;
@@ -570,7 +608,7 @@ extern "C" int jb_qkv_prepare_append(const float *qkv, int S, long long split_st
 #define JB_QPV(TC, LL)                                                                                  \
     launch(qkv_prepare_append_vec_kernel<TC, LL>, g, block, 0, st, qkv, S, (size_t)split_stride, ld, bias, \
            q_w, k_w, eps, cs, sn, rot_half, row_pos, row_seq, block_table, bt_stride, (TC *)q_out,       \
-           (TC *)k_cache, (TC *)v_cache, n, nh, nkv, hd, vd)
+           (TC *)k_cache, (TC *)v_cache, n, nh, nkv, hd, vd, mode)
 #define JB_QPV_L(TC)                                                                                    \
     do {                                                                                                \
         if (L == 8) JB_QPV(TC, 8);                                                                      \
@@ -589,11 +627,11 @@ extern "C" int jb_qkv_prepare_append(const float *qkv, int S, long long split_st
     if (cache_dt == JB_F32)
         launch(qkv_prepare_append_kernel<float>, grid, block, 0, st, qkv, S, (size_t)split_stride, ld, bias,
                q_w, k_w, eps, cs, sn, rot_half, row_pos, row_seq, block_table, bt_stride, (float *)q_out,
-               (float *)k_cache, (float *)v_cache, n, nh, nkv, hd, vd);
+               (float *)k_cache, (float *)v_cache, n, nh, nkv, hd, vd, mode);
     else if (cache_dt == JB_BF16)
         launch(qkv_prepare_append_kernel<bf16>, grid, block, 0, st, qkv, S, (size_t)split_stride, ld, bias,
                q_w, k_w, eps, cs, sn, rot_half, row_pos, row_seq, block_table, bt_stride, (bf16 *)q_out,
-               (bf16 *)k_cache, (bf16 *)v_cache, n, nh, nkv, hd, vd);
+               (bf16 *)k_cache, (bf16 *)v_cache, n, nh, nkv, hd, vd, mode);
     else
         return JB_EINVAL;
     return launch_status();

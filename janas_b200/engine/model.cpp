@@ -49,6 +49,9 @@ TensorList DecoderModel::top_tensors() const {
     if (!spec.position_table_name.empty())
         t.emplace_back(spec.position_table_name,
                        TensorSpec{{spec.max_positions, spec.hidden_size}, EMBEDDING, false});
+    if (!spec.token_table_name.empty())
+        t.emplace_back(spec.token_table_name,
+                       TensorSpec{{spec.vocab_size, spec.token_table_width}, EMBEDDING, false});
     if (embedding_norm) embedding_norm->tensors(spec.embedding_norm_name, t);
     final_norm->tensors(spec.final_norm_name, t);
     t.emplace_back(spec.head_name, TensorSpec{{spec.vocab_size, spec.hidden_size}, MATRIX, spec.tie_embeddings});
@@ -59,6 +62,7 @@ TensorList DecoderModel::tensors() const {
     TensorList top = top_tensors();
     TensorList t;
     size_t first = spec.position_table_name.empty() ? 1 : 2;     // the tables come first
+    if (!spec.token_table_name.empty()) first++;
     if (embedding_norm) {
         TensorList en;
         embedding_norm->tensors(spec.embedding_norm_name, en);
@@ -79,6 +83,7 @@ TensorList DecoderModel::tensors() const {
 void DecoderModel::load_top(TensorMap &t) {
     embedding = Part::take(t, spec.embedding_name);
     if (!spec.position_table_name.empty()) position_table = Part::take(t, spec.position_table_name);
+    if (!spec.token_table_name.empty()) token_table = Part::take(t, spec.token_table_name);
     auto it = t.find(spec.head_name);
     if (it != t.end()) {
         head = it->second;
@@ -149,7 +154,7 @@ void DecoderModel::load_random(unsigned long long seed) {
 }
 
 size_t DecoderModel::weight_bytes() const {
-    size_t total = head.bytes();
+    size_t total = head.bytes() + token_table.bytes();
     std::set<int> used;
     for (auto &e : spec.run_order) used.insert(e.layer);
     for (int layer : used) {
@@ -209,6 +214,8 @@ Buf DecoderModel::forward(StepContext &ctx, const int32_t *tokens, std::vector<L
                                 position_table.shape.at(0)));
     Buf x = ops::embed(d, embedding, tokens, n, position_table ? &position_table : nullptr, ctx.row_pos);
     if (spec.embedding_scale != 1.0) ops::scale_(d, x.as<float>(), n * spec.hidden_size, (float)spec.embedding_scale);
+    ctx.tokens = tokens;
+    ctx.token_table = token_table ? &token_table : nullptr;
     Stack pending;
     ctx.normed.reset();
     ctx.normed_by = nullptr;

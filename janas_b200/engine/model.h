@@ -63,7 +63,7 @@ public:
     Device *dev;
     std::vector<std::unique_ptr<Block>> blocks;
     std::unique_ptr<Norm> final_norm, embedding_norm;
-    DevTensor embedding, head, position_table;
+    DevTensor embedding, head, position_table, token_table;
     bool loaded = false;
 
 private:

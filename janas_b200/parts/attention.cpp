@@ -188,15 +188,23 @@ private:
 // are no softmax: with score_bias the weight of a visible key is
 // sigmoid(s_ij + score_bias_a), a learned number per head, not normalized over the keys.
 //
+// And: a short causal convolution over time on every column of q, k and v, directly after
+// the products (conv_taps; weights [columns, taps] beside each matrix, no bias; the last
+// taps - 1 sums of a sequence are its state); a position part of kind rope_pairs turns
+// neighbours (2i, 2i + 1); qk_unit_norm_eps: q and k are divided by their root mean square per
+// head AFTER the rotation, without a weight; gate: the joined heads are multiplied by
+// sigmoid(Wg h) before the output product (Wg's rows go into the q, k, v product).
+//
 // params: hidden_size, num_heads, num_kv_heads, head_dim, v_head_dim (default: head_dim),
 // scale (default 1/sqrt(head_dim)), window (0: none), keep_first (0: none), qk_norm_eps
-// (absent: no q/k norm), position (a part; absent: none), score_bias (boolean),
+// (absent: no q/k norm), qk_unit_norm_eps (absent: none), conv_taps (0: none), gate (boolean),
+// position (a part; absent: none), score_bias (boolean),
 // softcap (0 or absent: none),
 // distance_slope_exponent (absent: no bias), q_temp_coef and q_temp_every (absent or
 // every = 0: none), bias (on q, k, v), out_bias (on o; default: as bias), head_scale, sink, own_kv
 // (booleans; own_kv false: the run order gives this layer another entry's cache and it
 // has no key and value products), names (optional): q, k, v, o, bias (a suffix),
-// head_scale, sink, q_norm, k_norm, score_bias.
+// head_scale, sink, q_norm, k_norm, score_bias, gate, conv (a suffix).
 class SinkAttention : public Mixer {
 public:
     SinkAttention(const PartSpec &s, DType dt, Device *d) : Mixer(s, dt, d) {
@@ -237,7 +245,17 @@ public:
                 config_error(fmt("sink_attention: rotary_dim %d is above the head size %d", position_->rotary_dim(),
                                  g_.hd));
         }
-        prepared_ = qk_norm_ || (position_ && position_->rotary_dim() > 0);
+        gate_ = flag(s, "gate", false);
+        conv_taps_ = (int)s.get_int("conv_taps", 0);
+        if (conv_taps_ < 0) config_error("sink_attention: conv_taps must not be negative");
+        unit_norm_ = s.has("qk_unit_norm_eps");
+        if (unit_norm_) {
+            if (qk_norm_) config_error("sink_attention: a q/k norm with weights and one without are not built together");
+            qk_eps_ = (float)s.get_double("qk_unit_norm_eps");
+        }
+        if (conv_taps_ > 0 && (bias_ || !own_kv_))
+            config_error("sink_attention: the convolutions over q, k and v take no bias and need keys and values of the layer's own");
+        prepared_ = qk_norm_ || unit_norm_ || conv_taps_ > 0 || (position_ && position_->rotary_dim() > 0);
         if (prepared_ && q_every_ > 0)
             config_error("sink_attention: a query temperature together with a q/k norm or a rotation is not built");
         if (prepared_ && !own_kv_)
@@ -256,6 +274,8 @@ public:
         n_bias_ = leaf("bias", ".bias");
         n_hs_ = leaf("head_scale", "head_scale");
         n_sink_ = leaf("sink", "sink");
+        n_gate_ = leaf("gate", "g_proj.weight");
+        n_conv_ = leaf("conv", ".conv");
     }
 
     void tensors(const std::string &p, TensorList &out) const override {
@@ -277,6 +297,12 @@ public:
             out.emplace_back(name(p, n_kn_), TensorSpec{{g_.hd}, PARAM, false, 1.0f, 0.1f});
         }
         if (score_bias_) out.emplace_back(name(p, n_sb_), TensorSpec{{g_.nh}, PARAM, false, -2.0f, 0.5f});
+        if (gate_) out.emplace_back(name(p, n_gate_), TensorSpec{{ow, hidden_}, MATRIX, false});
+        if (conv_taps_ > 0) {
+            out.emplace_back(name(p, n_q_ + n_conv_), TensorSpec{{qw, conv_taps_}, PARAM, false, 0.25f, 0.25f});
+            out.emplace_back(name(p, n_k_ + n_conv_), TensorSpec{{kw, conv_taps_}, PARAM, false, 0.25f, 0.25f});
+            out.emplace_back(name(p, n_v_ + n_conv_), TensorSpec{{vw, conv_taps_}, PARAM, false, 0.25f, 0.25f});
+        }
         mat(n_o_, hidden_, ow, out_bias_);
         if (position_) position_->tensors(name(p, "position"), out);
     }
@@ -291,7 +317,17 @@ public:
             in.push_back(take(t, name(p, n_v_)));
             if (bias_) bs.push_back(take(t, name(p, n_v_ + n_bias_)));
         }
+        if (gate_) {
+            gate_col0_ = 0;
+            for (auto &m : in) gate_col0_ += m.shape[0];
+            in.push_back(take(t, name(p, n_gate_)));       // the gate reads what q, k and v read
+        }
         w_in_ = fuse_rows(*dev, in);
+        if (conv_taps_ > 0) {
+            std::vector<DevTensor> cw = {take(t, name(p, n_q_ + n_conv_)), take(t, name(p, n_k_ + n_conv_)),
+                                         take(t, name(p, n_v_ + n_conv_))};
+            conv_w_ = fuse_rows(*dev, cw);
+        }
         if (bias_) {
             // one bias vector over the fused product's columns
             for (auto &b : bs) b.shape = {b.numel(), 1};
@@ -333,8 +369,15 @@ public:
 
     size_t weight_bytes() const override {
         return w_in_.bytes() + w_o_.bytes() + b_in_.bytes() + b_o_.bytes() + temp_.bytes() + sinks_.bytes() +
-               q_norm_.bytes() + k_norm_.bytes() + score_b_.bytes();
+               q_norm_.bytes() + k_norm_.bytes() + score_b_.bytes() + conv_w_.bytes();
     }
+
+    // the convolutions' last taps - 1 inputs: the products' sums of q, k and v
+    long long conv_width() const { return (long long)g_.nh * g_.hd + (long long)g_.nkv * (g_.hd + g_.vd); }
+    StateSpec state_spec() const override {
+        return conv_taps_ > 1 ? StateSpec{{conv_taps_ - 1, conv_width()}, F32} : StateSpec();
+    }
+    bool strided_state() const override { return true; }
 
     KVSpec kv_spec() const override {
         return own_kv_ ? KVSpec{g_.nkv, g_.hd, g_.window, g_.vd, false, g_.keep_first} : KVSpec();
@@ -381,35 +424,65 @@ public:
         max_chunks += ops::attention_kept_chunks(g_.window, g_.keep_first);
         bool decode = ctx.kind == DECODE;
         if (prepared_) {
-            // bias, per-head norms and the rotation in one pass over the product's sums, K and V
-            // into the cache; then attention over the cache
+            // (the convolutions over time,) bias, per-head norms and the rotation in one pass over
+            // the product's sums, K and V into the cache; then attention over the cache
+            Stack conv;
+            if (conv_taps_ > 0) conv = convolve(ctx, qkv, cache);
             int rot = position_ ? position_->rotary_dim() : 0;
-            Buf q = ops::qkv_prepare_append(d, qkv, b_in, qk_norm_ ? (const float *)q_norm_.ptr : nullptr,
+            Buf q = ops::qkv_prepare_append(d, conv ? conv : qkv, b_in, qk_norm_ ? (const float *)q_norm_.ptr : nullptr,
                                             qk_norm_ ? (const float *)k_norm_.ptr : nullptr, qk_eps_,
                                             rot ? position_->cos() : nullptr, rot ? position_->sin() : nullptr,
-                                            rot / 2, ctx.row_pos, ctx.row_seq, cache.kv, g_, ctx.dtype);
-            keep_side(ctx, qkv);
+                                            rot / 2, ctx.row_pos, ctx.row_seq, cache.kv, g_, ctx.dtype,
+                                            rot && position_->pairs(), unit_norm_);
+            conv = Stack();
             const int32_t *blocks = prefill_blocks(ctx, decode);
             Buf a = ops::attention(d, q.ptr, n, cache.kv, g_, ctx.row_pos, ctx.row_seq, max_chunks, blocks,
                                    n_blocks_, decode);
-            return output(ctx, a);
+            return finish(ctx, qkv, a);
         }
         if (decode && ctx.dtype == BF16 && q_every_ == 0 && !g_.keep_first && !score_bias_) {
             // one new token per sequence: the attention kernel makes q and the new key and
             // value from the product's sums and its bias itself, where it takes the sizes
             Buf a = ops::attention_decode_qkv(d, qkv, nullptr, nullptr, 0.0f, nullptr, nullptr, cache.kv, g_,
                                               ctx.row_pos, ctx.row_seq, max_chunks, b_in);
-            if (a) {
-                keep_side(ctx, qkv);
-                return output(ctx, a);
-            }
+            if (a) return finish(ctx, qkv, a);
         }
         Buf q = ops::qkv_bias_append(d, qkv, b_in, ctx.row_pos, ctx.row_seq, cache.kv, g_, ctx.dtype, own_kv_,
                                      q_coef_, q_every_);
-        keep_side(ctx, qkv);
         const int32_t *blocks = prefill_blocks(ctx, decode);
         Buf a = ops::attention(d, q.ptr, n, cache.kv, g_, ctx.row_pos, ctx.row_seq, max_chunks, blocks, n_blocks_,
                                decode);
+        return finish(ctx, qkv, a);
+    }
+
+    // q, k and v through their convolutions over time, as one sum [n, q + k + v] in float32;
+    // the state holds each sequence's last taps - 1 sums.
+    Stack convolve(StepContext &ctx, const Stack &qkv, LayerCache &cache) {
+        long long C = conv_width();
+        long long stride = cache.state_stride > 0 ? cache.state_stride : (long long)(conv_taps_ - 1) * C;
+        if (conv_taps_ > 1 && (!cache.state || cache.state_spec.bytes() < state_spec().bytes()))
+            fail(JB_LLM_EINVAL, "sink_attention: the cache holds no state for the layer's convolutions");
+        float *st = (float *)cache.state;
+        Stack out;
+        out.S = 1;
+        out.n = ctx.n_rows;
+        out.m = C;
+        const float *w = (const float *)conv_w_.ptr;
+        // rows that read sums of earlier steps which other rows of this step replace: two launches
+        bool two = ctx.kind == EXTEND && conv_taps_ > 1;
+        out.buf = ops::causal_conv(*ctx.dev, qkv, 0, C, w, nullptr, conv_taps_, st, stride, ctx.row_pos, ctx.row_seq,
+                                   ctx.seq_slot, false, F32, true, !two);
+        if (two)
+            ops::causal_conv(*ctx.dev, qkv, 0, C, w, nullptr, conv_taps_, st, stride, ctx.row_pos, ctx.row_seq,
+                             ctx.seq_slot, false, F32, false, true);
+        return out;
+    }
+
+    // the heads' outputs times the gate's sigmoid (where there is one), then the output product
+    Stack finish(StepContext &ctx, Stack &qkv, Buf &a) {
+        if (gate_)
+            a = ops::gate_rows(*ctx.dev, a.ptr, ctx.dtype, ctx.n_rows, (long long)g_.nh * g_.vd, qkv, gate_col0_);
+        keep_side(ctx, qkv);
         return output(ctx, a);
     }
 
@@ -465,6 +538,11 @@ private:
     bool bias_, out_bias_, head_scale_, sink_, own_kv_;
     bool qk_norm_ = false, score_bias_ = false;
     bool prepared_ = false;      // q and k are normed or rotated: qkv_prepare_append makes them
+    bool gate_ = false, unit_norm_ = false;
+    int conv_taps_ = 0;
+    long long gate_col0_ = 0;
+    std::string n_gate_, n_conv_;
+    DevTensor conv_w_;
     float qk_eps_ = 0.0f;
     std::unique_ptr<PositionEncoding> position_;
     DevTensor q_norm_, k_norm_, score_b_;

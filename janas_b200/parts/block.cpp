@@ -84,7 +84,9 @@ private:
 // block_params: hidden_size; mixer_gate / ffn_gate: the tensor names (below the
 // layer's prefix) of the gates' matrices [hidden, hidden], absent or null for no
 // gate; gate_bias: the suffix of a gate's bias vector ("" for none); fuse (default
-// true): false runs gate, norm and add as kernels of their own.
+// true): false runs gate, norm and add as kernels of their own; token_side (optional):
+// {dim, col0, eps, names {gate, proj, norm}}: an input of the token's own after the sublayers,
+// from columns col0 .. col0 + dim - 1 of the model's token table (see token_side()).
 class SandwichBlock : public Block {
 public:
     SandwichBlock(BlockParts p, const LayerSpec &ls, DType dt, Device *d) : Block(std::move(p)), dev_(d) {
@@ -98,6 +100,21 @@ public:
         if (bp.get("ffn_gate").is_string() && feed_forward) gate_name_[1] = bp.get("ffn_gate").as_string();
         if (bp.get("gate_bias").is_string()) bias_suffix_ = bp.get("gate_bias").as_string();
         if (bp.get("fuse").is_bool()) fuse_ = bp.get("fuse").as_bool();
+        const Json &ts = bp.get("token_side");
+        if (ts.is_object()) {
+            PartSpec tp{"sandwich: token_side", ts};
+            side_dim_ = tp.get_int("dim");
+            side_col0_ = tp.get_int("col0", 0);
+            side_eps_ = (float)tp.get_double("eps");
+            if (side_dim_ <= 0 || side_col0_ < 0) config_error("sandwich: token_side needs dim > 0 and col0 >= 0");
+            const Json &nm = ts.get("names");
+            auto leaf = [&](const char *key, const char *dflt) {
+                return nm.is_object() && nm.get(key).is_string() ? nm.get(key).as_string() : std::string(dflt);
+            };
+            side_name_[0] = leaf("gate", "side.gate");
+            side_name_[1] = leaf("proj", "side.proj");
+            side_name_[2] = leaf("norm", "side.norm");
+        }
         // tensors of an absent feed-forward's surroundings that a file may still
         // hold: tolerated and not read
         if (!feed_forward)
@@ -117,6 +134,11 @@ public:
                 out.emplace_back(Part::name(prefix, gate_name_[i] + bias_suffix_),
                                  TensorSpec{{hidden_}, PARAM, false, 0.0f, 0.02f});
         }
+        if (side_dim_ > 0) {
+            out.emplace_back(Part::name(prefix, side_name_[0]), TensorSpec{{side_dim_, hidden_}, MATRIX, false});
+            out.emplace_back(Part::name(prefix, side_name_[1]), TensorSpec{{hidden_, side_dim_}, MATRIX, false});
+            out.emplace_back(Part::name(prefix, side_name_[2]), TensorSpec{{hidden_}, PARAM, false, 1.0f, 0.1f});
+        }
         for (auto &u : unused_)
             out.emplace_back(Part::name(prefix, u.first),
                              TensorSpec{u.second, u.second.size() == 2 ? MATRIX : PARAM, true});
@@ -133,12 +155,15 @@ public:
                 in_part_[i] = p->take_side_rows(gate_[i]);
             }
         }
+        if (side_dim_ > 0)
+            for (int i = 0; i < 3; i++) side_w_[i] = Part::take(t, Part::name(prefix, side_name_[i]));
         for (auto &u : unused_) t.erase(Part::name(prefix, u.first));
     }
 
     size_t weight_bytes() const override {
         // a gate that went into its sublayer's first product is counted there
-        return gate_[0].bytes() + gate_[1].bytes() + gate_bias_[0].bytes() + gate_bias_[1].bytes();
+        return gate_[0].bytes() + gate_[1].bytes() + gate_bias_[0].bytes() + gate_bias_[1].bytes() +
+               side_w_[0].bytes() + side_w_[1].bytes() + side_w_[2].bytes();
     }
 
     void forward(StepContext &ctx, float *x, Stack &pending, LayerCache &cache) override {
@@ -151,18 +176,23 @@ public:
             Stack g = gate_product(ctx, 0, h.ptr);
             Stack y = mixer->forward(ctx, h.ptr, cache);
             long long col0 = take_side(ctx, 0, g);
-            const Norm *next = feed_forward ? ffn_norm.get() : next_norm;
+            // what the token's own input changes afterwards cannot be normed ahead
+            const Norm *next = feed_forward ? ffn_norm.get() : side_dim_ > 0 ? nullptr : next_norm;
             finish(ctx, x, y, g, col0, 0, post_mixer_norm.get(), next);
         }
-        if (!feed_forward) return;
+        if (!feed_forward) {
+            token_side(ctx, x);
+            return;
+        }
         h = take_normed(ctx, ffn_norm.get());
         if (!h) h = ffn_norm->apply(ctx, x, n, ctx.dtype, nullptr, nullptr, 0);
         {
             Stack g = gate_product(ctx, 1, h.ptr);
             Stack y = feed_forward->forward(ctx, h.ptr);
             long long col0 = take_side(ctx, 1, g);
-            finish(ctx, x, y, g, col0, 1, post_ffn_norm.get(), next_norm);
+            finish(ctx, x, y, g, col0, 1, post_ffn_norm.get(), side_dim_ > 0 ? nullptr : next_norm);
         }
+        token_side(ctx, x);
     }
 
 private:
@@ -207,6 +237,13 @@ private:
             }
             return;
         }
+        ops::LnParams lp;
+        bool rms = false;
+        if (fuse_ && !g && post->layer_norm(&lp, &rms)) {
+            // no gate and a norm whose kernel adds its result: sums, norm and add in one pass
+            ops::norm_residual_(d, x, y, lp, rms, ctx.kind == DECODE && ctx.dtype == BF16);
+            return;
+        }
         // the steps one by one, for any norm: gate, norm of the result, add
         Buf t;
         Stack one;
@@ -224,8 +261,41 @@ private:
         ops::add_(d, x, n, hidden_, one);
     }
 
+    // The token's own input to the layer, after the sublayers: with e = the token's row of the
+    // model's token table, columns col0 .. col0 + dim - 1,
+    //   y = P (gelu_tanh(G x) * e);   x += rms(y) w        (a plain weight, eps inside the root)
+    void token_side(StepContext &ctx, float *x) {
+        if (side_dim_ <= 0) return;
+        Device &d = *ctx.dev;
+        long long n = ctx.n_rows;
+        if (!ctx.token_table || !ctx.tokens)
+            fail(JB_LLM_EINVAL, "sandwich: the model has no token table for the layers' token input");
+        if (side_col0_ + side_dim_ > ctx.token_table->shape.at(1))
+            fail(JB_LLM_EINVAL, "sandwich: the layer's columns lie outside the token table");
+        Buf hx;
+        const void *in = x;
+        if (ctx.dtype != F32) {
+            hx = d.pool.get((size_t)n * (size_t)hidden_ * dtype_size(ctx.dtype));
+            if (jb_convert(x, F32, hx.ptr, ctx.dtype, n * hidden_, d.stream) != 0)
+                fail(JB_LLM_EFAIL, "sandwich: the conversion could not be launched");
+            in = hx.ptr;
+        }
+        Stack P = ops::linear(d, in, ctx.dtype, n, hidden_, side_w_[0]);
+        Buf gt = ops::token_gate(d, P, *ctx.token_table, side_col0_, side_dim_, ctx.tokens, ctx.dtype);
+        P = Stack();
+        Stack y = ops::linear(d, gt.ptr, ctx.dtype, n, side_dim_, side_w_[1]);
+        ops::LnParams lp;
+        lp.w = (const float *)side_w_[2].ptr;
+        lp.eps = side_eps_;
+        ops::norm_residual_(d, x, y, lp, true, ctx.kind == DECODE && ctx.dtype == BF16);
+    }
+
     Device *dev_;
     long long hidden_ = 0;
+    long long side_dim_ = 0, side_col0_ = 0;
+    float side_eps_ = 0.0f;
+    std::string side_name_[3];
+    DevTensor side_w_[3];
     bool fuse_ = true;      // false: every step as a kernel of its own (for comparisons)
     std::string gate_name_[2], bias_suffix_;
     DevTensor gate_[2], gate_bias_[2];

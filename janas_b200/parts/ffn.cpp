@@ -8,7 +8,7 @@ namespace jb {
 
 namespace {
 
-// params: hidden_size, intermediate_size
+// params: hidden_size, intermediate_size, names (optional): gate, up, down
 class SwiGLU : public FeedForward {
 public:
     // Rows from which gate, up and the activation run as one kernel.  Measured on
@@ -26,19 +26,25 @@ public:
         hidden_ = s.get_int("hidden_size");
         inter_ = s.get_int("intermediate_size");
         if (hidden_ <= 0 || inter_ <= 0) config_error("swiglu: sizes must be positive");
+        const Json &nm = s.params.get("names");
+        auto leaf = [&](const char *key, const char *dflt) {
+            return nm.is_object() && nm.get(key).is_string() ? nm.get(key).as_string() : std::string(dflt);
+        };
+        n_gate_ = leaf("gate", "gate_proj.weight");
+        n_up_ = leaf("up", "up_proj.weight");
+        n_down_ = leaf("down", "down_proj.weight");
     }
 
     void tensors(const std::string &prefix, TensorList &out) const override {
-        out.emplace_back(name(prefix, "gate_proj.weight"), TensorSpec{{inter_, hidden_}, MATRIX, false});
-        out.emplace_back(name(prefix, "up_proj.weight"), TensorSpec{{inter_, hidden_}, MATRIX, false});
-        out.emplace_back(name(prefix, "down_proj.weight"), TensorSpec{{hidden_, inter_}, MATRIX, false});
+        out.emplace_back(name(prefix, n_gate_), TensorSpec{{inter_, hidden_}, MATRIX, false});
+        out.emplace_back(name(prefix, n_up_), TensorSpec{{inter_, hidden_}, MATRIX, false});
+        out.emplace_back(name(prefix, n_down_), TensorSpec{{hidden_, inter_}, MATRIX, false});
     }
 
     void load(const std::string &prefix, TensorMap &t) override {
-        std::vector<DevTensor> gu = {take(t, name(prefix, "gate_proj.weight")),
-                                     take(t, name(prefix, "up_proj.weight"))};
+        std::vector<DevTensor> gu = {take(t, name(prefix, n_gate_)), take(t, name(prefix, n_up_))};
         w_gate_up_ = fuse_rows(*dev, gu);
-        w_down_ = take(t, name(prefix, "down_proj.weight"));
+        w_down_ = take(t, name(prefix, n_down_));
     }
 
     size_t weight_bytes() const override { return w_gate_up_.bytes() + w_down_.bytes(); }
@@ -72,6 +78,7 @@ public:
 
 private:
     long long hidden_, inter_;
+    std::string n_gate_, n_up_, n_down_;
     DevTensor w_gate_up_, w_down_;
     bool fused_last_ = false;      // whether the last forward took the one-kernel way
 };

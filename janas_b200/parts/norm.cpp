@@ -6,20 +6,38 @@ namespace jb {
 
 namespace {
 
-// params: size, eps
+// params: size, eps; one_plus (default false): the stored weight lies around zero and the
+// norm multiplies by 1 + w (the sum is taken once, in float32, when the weight is loaded);
+// names (optional): weight: the tensor's leaf below the part's prefix ("" for the prefix itself)
 class RMSNorm : public Norm {
 public:
     RMSNorm(const PartSpec &s, DType dt, Device *d) : Norm(s, dt, d) {
         size_ = s.get_int("size");
         eps_ = (float)s.get_double("eps");
+        one_plus_ = s.has("one_plus") && s.params.get("one_plus").as_bool();
         if (size_ <= 0) config_error("rmsnorm: size must be positive");
+        const Json &nm = s.params.get("names");
+        w_name_ = nm.is_object() && nm.get("weight").is_string() ? nm.get("weight").as_string() : "weight";
     }
 
     void tensors(const std::string &prefix, TensorList &out) const override {
-        out.emplace_back(name(prefix, "weight"), TensorSpec{{size_}, NORM, false});
+        if (one_plus_) out.emplace_back(name(prefix, w_name_), TensorSpec{{size_}, PARAM, false, 0.0f, 0.1f});
+        else out.emplace_back(name(prefix, w_name_), TensorSpec{{size_}, NORM, false});
     }
 
-    void load(const std::string &prefix, TensorMap &t) override { weight_ = take(t, name(prefix, "weight")); }
+    void load(const std::string &prefix, TensorMap &t) override {
+        weight_ = take(t, name(prefix, w_name_));
+        if (one_plus_) {
+            if (weight_.dt != F32) fail(JB_LLM_EFAIL, "rmsnorm: a weight around zero is kept in float32");
+            std::vector<float> host((size_t)size_);
+            dev->sync();
+            cuda_check(cudaMemcpy(host.data(), weight_.ptr, host.size() * 4, cudaMemcpyDeviceToHost),
+                       "reading a norm's weight");
+            for (float &v : host) v = 1.0f + v;
+            cuda_check(cudaMemcpy(weight_.ptr, host.data(), host.size() * 4, cudaMemcpyHostToDevice),
+                       "writing a norm's weight");
+        }
+    }
 
     size_t weight_bytes() const override { return weight_.bytes(); }
 
@@ -29,6 +47,16 @@ public:
     }
 
     long long size() const override { return size_; }
+
+    // a float32 weight can go into the kernel that norms a sublayer's result and adds it
+    bool layer_norm(ops::LnParams *out, bool *rms) const override {
+        if (!weight_ || weight_.dt != F32) return false;
+        out->w = (const float *)weight_.ptr;
+        out->b = nullptr;
+        out->eps = eps_;
+        *rms = true;
+        return true;
+    }
 
     Json info() const override {
         Json o = Json::object();
@@ -41,6 +69,8 @@ public:
 private:
     long long size_;
     float eps_;
+    bool one_plus_ = false;
+    std::string w_name_;
     DevTensor weight_;
 };
 

@@ -47,6 +47,9 @@ struct LayerCache {
     int kv_heads = 0, head_dim = 0, v_head_dim = 0;
     void *state = nullptr;              // [slots, *state shape], indexed by slot; or null
     StateSpec state_spec;
+    // floats from one slot's state to the next's where the state is a part of a longer row
+    // per slot (a mixer that is one of a pair); 0: the state's own size
+    long long state_stride = 0;
     void *block_state = nullptr;        // the block arrangement's own state, [slots, *shape]; or null
     StateSpec block_state_spec;
     int n_slots = 0;
@@ -70,6 +73,10 @@ struct StepContext {
     std::vector<long long> seq_pos0;     // tokens each sequence had before the step
     std::vector<long long> seq_len;      // tokens each sequence brings
     std::vector<long long> seq_row0;     // first row of each sequence (n_seqs + 1 values)
+    const int32_t *tokens = nullptr;     // the rows' token ids, on the device
+    // a table of vectors per token beside the embedding (ModelSpec::token_table_name), for
+    // blocks that give every layer an input of the token's own; null: the model has none
+    const DevTensor *token_table = nullptr;
     long long max_pos = 0;               // the largest position of any row (a bound, in a captured step)
     bool captured = false;               // the launches are being recorded into a graph
     // For finding the first layer that goes wrong: when set, the model copies the
@@ -158,6 +165,8 @@ public:
     virtual const float *cos() const { return nullptr; }     // [n_positions, rotary_dim / 2] or null
     virtual const float *sin() const { return nullptr; }
     virtual int rotary_dim() const { return 0; }
+    // true: angle i turns the neighbours (2i, 2i + 1); false: values i and i + rotary_dim / 2
+    virtual bool pairs() const { return false; }
     virtual long long n_positions() const { return 1ll << 62; }
 };
 
@@ -168,6 +177,8 @@ public:
     virtual KVSpec kv_spec() const { return KVSpec(); }
     // Fixed-size state per sequence (none() for nothing).
     virtual StateSpec state_spec() const { return StateSpec(); }
+    // whether the mixer honours LayerCache::state_stride (it can then be one of a pair)
+    virtual bool strided_state() const { return false; }
     virtual void prepare(long long n_positions) {}
     // Whether the mixer can run a step of this kind.
     virtual bool supports(StepKind kind) const { return true; }
@@ -263,6 +274,7 @@ void register_builtin_feed_forwards();
 void register_builtin_blocks();
 void register_recurrent_mixers();
 void register_routed_feed_forwards();
+void register_pair_mixers();
 
 }  // namespace jb
 

@@ -29,6 +29,7 @@ Tables &ready() {
         register_builtin_blocks();
         register_recurrent_mixers();
         register_routed_feed_forwards();
+        register_pair_mixers();
     });
     return raw();
 }

@@ -24,10 +24,10 @@ namespace jb {
 
 namespace {
 
-// params: rotary_dim, theta, max_positions
+// params: rotary_dim, theta, max_positions, scaling (optional): {factor, low, high, original}
 class RopeNeox : public PositionEncoding {
 public:
-    RopeNeox(const PartSpec &s, DType dt, Device *d, bool pairs = false) : PositionEncoding(s, dt, d) {
+    RopeNeox(const PartSpec &s, DType dt, Device *d, bool pairs = false) : PositionEncoding(s, dt, d), pairs_(pairs) {
         rotary_dim_ = (int)s.get_int("rotary_dim");
         theta_ = s.get_double("theta");
         max_positions_ = s.get_int("max_positions");
@@ -39,6 +39,28 @@ public:
             float expo = -2.0f * (float)i / (float)rotary_dim_;
             inv_freq_[(size_t)i] = pairs ? (float)std::pow(theta_, -2.0 * (double)i / (double)rotary_dim_)
                                          : (float)std::pow((double)(float)theta_, (double)expo);
+        }
+        if (s.has("scaling")) {
+            // long wavelengths are stretched: with l = 2 pi / f, f stays where l < original / high,
+            // becomes f / factor where l > original / low, and in between is the mix
+            // (1 - t) f / factor + t f with t = (original / l - low) / (high - low)
+            PartSpec sc{"", s.params.get("scaling")};
+            double factor = sc.get_double("factor"), low = sc.get_double("low"), high = sc.get_double("high");
+            double original = sc.get_double("original");
+            if (factor <= 0 || original <= 0 || low <= 0 || high <= low)
+                config_error("rope: scaling needs factor > 0, original > 0 and 0 < low < high");
+            const double two_pi = 6.283185307179586476925286766559;
+            for (int i = 0; i < half; i++) {
+                double f = std::pow(theta_, -2.0 * (double)i / (double)rotary_dim_);
+                double wavelength = two_pi / f;
+                if (wavelength > original / low) {
+                    f = f / factor;
+                } else if (!(wavelength < original / high)) {
+                    double t = (original / wavelength - low) / (high - low);
+                    f = (1.0 - t) * f / factor + t * f;
+                }
+                inv_freq_[(size_t)i] = (float)f;
+            }
         }
     }
 
@@ -62,6 +84,7 @@ public:
     const float *cos() const override { return (const float *)cos_.ptr; }
     const float *sin() const override { return (const float *)sin_.ptr; }
     int rotary_dim() const override { return rotary_dim_; }
+    bool pairs() const override { return pairs_; }
     long long n_positions() const override { return n_; }
 
     Json info() const override {
@@ -75,6 +98,7 @@ public:
 
 private:
     int rotary_dim_;
+    bool pairs_ = false;
     double theta_;
     long long max_positions_;
     std::vector<float> inv_freq_;

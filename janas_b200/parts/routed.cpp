@@ -30,8 +30,11 @@ namespace {
 // params: hidden_size, experts, expert_ff, identity (default 0), top, groups (default 1),
 // group_keep (default groups), scale (default 1), correction (default false: a vector
 // added to the scores for the choice alone), shared_ff (default 0: no shared expert),
-// activation ("relu2", "relu", "gelu_tanh"), names (optional): expert (a prefix, the
-// expert's index follows), up, down, router, correction, shared
+// activation ("relu2", "relu", "gelu_tanh", "silu"), gated (default false: an expert is
+// Wd (act(Wg h) * (Wu h)) with a gate matrix of its own), score ("softmax", the default, or
+// "sigmoid": each score the sigmoid of its own logit), group_best (default 1: a group's score
+// is the sum of this many of its largest choice scores), names (optional): expert (a prefix,
+// the expert's index follows), gate, up, down, router, correction, shared
 class RoutedFFN : public FeedForward {
 public:
     RoutedFFN(const PartSpec &s, DType dt, Device *d) : FeedForward(s, dt, d) {
@@ -47,7 +50,14 @@ public:
         shared_ff_ = s.get_int("shared_ff", 0);
         std::string act = s.params.get("activation").is_string() ? s.params.get("activation").as_string() : "";
         act_ = ops::activation_kind(act);
-        if (act_ < 0) config_error("routed: activation '" + act + "' is not one of relu2, relu, gelu_tanh");
+        if (act_ < 0) config_error("routed: activation '" + act + "' is not one of relu2, relu, gelu_tanh, silu");
+        gated_ = s.has("gated") && s.params.get("gated").as_bool();
+        std::string score = s.params.get("score").is_string() ? s.params.get("score").as_string() : "softmax";
+        if (score != "softmax" && score != "sigmoid") config_error("routed: score '" + score + "' is not softmax or sigmoid");
+        sigmoid_ = score == "sigmoid";
+        group_best_ = s.get_int("group_best", 1);
+        if (group_best_ < 1) config_error("routed: group_best must be positive");
+        if (gated_ && s.get_int("shared_ff", 0) > 0) config_error("routed: experts with a gate and a shared expert together are not built");
         long long outs = experts_ + identity_;
         if (hidden_ <= 0 || experts_ < 0 || identity_ < 0 || outs <= 0 || (experts_ > 0 && ff_ <= 0) ||
             shared_ff_ < 0)
@@ -67,15 +77,18 @@ public:
         n_router_ = leaf("router", "router.weight");
         n_corr_ = leaf("correction", "router.correction");
         n_shared_ = leaf("shared", "shared");
+        n_gate_ = leaf("gate", "gate_proj.weight");
         // the columns of the first product: experts, shared expert, padding to a
         // multiple of 8 (so that every row of sums can be read four values at a time), router
         act_width_ = experts_ * ff_ + shared_ff_;
-        router_col0_ = (act_width_ + 7) / 8 * 8;
+        up_width_ = gated_ ? 2 * experts_ * ff_ : act_width_;
+        router_col0_ = (up_width_ + 7) / 8 * 8;
     }
 
     void tensors(const std::string &p, TensorList &out) const override {
         for (long long e = 0; e < experts_; e++) {
             std::string ep = name(p, n_expert_ + std::to_string(e));
+            if (gated_) out.emplace_back(name(ep, n_gate_), TensorSpec{{ff_, hidden_}, MATRIX, false});
             out.emplace_back(name(ep, n_up_), TensorSpec{{ff_, hidden_}, MATRIX, false});
             out.emplace_back(name(ep, n_down_), TensorSpec{{hidden_, ff_}, MATRIX, false});
         }
@@ -93,6 +106,7 @@ public:
         std::vector<DevTensor> ups, downs;
         for (long long e = 0; e < experts_; e++) {
             std::string ep = name(p, n_expert_ + std::to_string(e));
+            if (gated_) ups.push_back(take(t, name(ep, n_gate_)));      // per expert [gate | up]
             ups.push_back(take(t, name(ep, n_up_)));
             downs.push_back(take(t, name(ep, n_down_)));
         }
@@ -102,7 +116,7 @@ public:
             downs.push_back(take(t, name(sp, n_down_)));
         }
         DevTensor router = take(t, name(p, n_router_));
-        if (router_col0_ > act_width_) ups.push_back(dev->tensor(router.dt, {router_col0_ - act_width_, hidden_}, true));
+        if (router_col0_ > up_width_) ups.push_back(dev->tensor(router.dt, {router_col0_ - up_width_, hidden_}, true));
         ups.push_back(router);
         w_up_ = fuse_rows(*dev, ups);
         if (!downs.empty()) w_down_ = fuse_cols(*dev, downs);
@@ -123,12 +137,17 @@ public:
         r.first_identity = (int)experts_;
         r.scale = scale_;
         r.correction = correction_ ? (const float *)corr_.ptr : nullptr;
+        r.sigmoid_scores = sigmoid_;
+        r.group_best = (int)group_best_;
         Buf skip_coef;
         Buf weights = ops::moe_route(d, z, router_col0_, r, identity_ > 0 ? &skip_coef : nullptr);
         Stack out;
         if (act_width_ > 0) {
-            Buf act = ops::activation_weighted(d, z, act_width_, weights.as<float>(), (int)(experts_ + identity_),
-                                               (int)experts_, ff_, act_, ctx.dtype);
+            Buf act = gated_ ? ops::gated_weighted(d, z, weights.as<float>(), (int)(experts_ + identity_),
+                                                   (int)experts_, ff_, act_, ctx.dtype)
+                             : ops::activation_weighted(d, z, act_width_, weights.as<float>(),
+                                                        (int)(experts_ + identity_), (int)experts_, ff_, act_,
+                                                        ctx.dtype);
             z = Stack();
             out = ops::linear(d, act.ptr, ctx.dtype, n, act_width_, w_down_);
         } else {
@@ -159,7 +178,9 @@ public:
 
 private:
     long long hidden_, experts_, ff_, identity_, top_, groups_, keep_, shared_ff_;
-    long long act_width_ = 0, router_col0_ = 0;
+    long long act_width_ = 0, up_width_ = 0, router_col0_ = 0, group_best_ = 1;
+    bool gated_ = false, sigmoid_ = false;
+    std::string n_gate_;
     float scale_;
     bool correction_;
     int act_;
