@@ -10,6 +10,7 @@
     python bench.py --only zuzelorn [--layers 8]           (the Zuzelorn design beside Qwen3 at equal sizes)
     python bench.py --only dunavik [--design-size 4b]      (the Dunavik design beside Zuzelorn at equal sizes)
     python bench.py --only kefesun [--design-size 4b]      (the Kefesun design beside Dunavik's attention layers)
+    python bench.py --only munisun [--design-size 4b]      (the Munisun design beside Kefesun's mixed layers)
 
 The default run has the layer sizes of Qwen3-4B (36 layers, hidden 2560, 32
 heads, 8 KV heads, head size 128, feed-forward 9728, vocabulary 151936, tied
@@ -271,14 +272,17 @@ def decode_timeline(eng, slots, tokens, warmup):
 
 
 def step_bytes(eng, batch, context):
-    """Bytes a decode step has to read: every weight once, and the keys and
-    values of the live sequences."""
+    """Bytes a decode step has to move: every weight once, the keys and values of
+    the live sequences, and their recurrent state there and back."""
     info = eng.info()
     esz = 2 if info["dtype"] == "bfloat16" else 4
     kv = 0
     for g in info["cache"]["groups"]:
         per_token = 2 * len(g["entries"]) * g["num_kv_heads"] * g["head_dim"] * esz
         kv += per_token * batch * context
+    # the mixers' fixed-size state of every live sequence, read and written once a step
+    for b in info["cache"].get("state_bytes", []):
+        kv += 2 * b * batch
     return info["weight_bytes"] + kv
 
 
@@ -496,6 +500,74 @@ def kefesun_flops(cfg, tokens):
     return asked + head, run + head
 
 
+def munisun_cfg(size, n_layers, vocab, mixers="mixed"):
+    """A Munisun config.json of the given layer sizes.  mixers: "parallel" (every layer softmax
+    attention beside a Mamba-2 recurrence), "parallel2" (every layer softmax attention with
+    convolutions beside a linear attention with a decay) or "mixed" (the two in turn, the second
+    kind first).  Every second layer's feed-forward is routed and holds as many weights as the
+    dense one of the size: eight experts of an eighth of its width, two per token from two of four
+    groups.  The recurrences are as wide as the model: Mamba-2 heads of 64 values with a state of
+    128 rows in 8 groups, linear-attention heads of the size's head size."""
+    dm, nh, nkv, hd, ff = DESIGN_SIZES[size]
+    moe = {"expert": {"ff": ff // 8}, "kind": "moe",
+           "router": {"experts": 8, "groups": {"count": 4, "keep": 2}, "top": 2}}
+    layers = []
+    for i in range(n_layers):
+        left = {"dim": hd, "heads": nh, "kv_heads": nkv, "rot": {"base": 1000000.0, "dims": hd // 2},
+                "scale": hd ** -0.5, "vdim": hd}
+        mlp = moe if i % 2 else {"ff": ff, "kind": "dense"}
+        if mixers == "parallel" or (mixers == "mixed" and i % 2 == 1):
+            left["softcap"] = 50.0
+            left["rot"]["scaling"] = {"factor": 8.0, "high": 4.0, "low": 1.0, "original": 8192}
+            right = {"conv": 4, "groups": 8, "heads": dm // 64, "norm_groups": 8, "state": 128, "vdim": 64}
+            layers.append({"type": "parallel", "mlp": mlp,
+                           "mixer": {"left": left, "left_scale": 0.7, "right": right, "right_scale": 0.7}})
+        else:
+            left["conv"] = 4
+            lh = dm // hd
+            right = {"decay": [1.0 - 2.0 ** (-5.0 - 3.0 * a / max(1, lh - 1)) for a in range(lh)],
+                     "dim": hd, "heads": lh, "vdim": hd}
+            layers.append({"type": "parallel_2", "mlp": mlp, "mixer": {"left": left, "right": right}})
+    return {"architecture": "Munisun", "embedding": {"scale": 1.0}, "layers": layers, "norm": {"eps": 1e-5},
+            "token_side": {"dim": 64}, "vocab": vocab, "width": dm}
+
+
+def munisun_flops(cfg, tokens):
+    """Multiply-adds times two of one prompt of a Munisun model: (what the design asks for: the
+    chosen experts' products; what the engine runs: every expert's for every token).  Both with the
+    mixers' products, the attention over all earlier keys, the recurrences (a state of N x P values
+    per head read and written once a token: 4 N P per head) and the head for one row."""
+    dm, asked, run = cfg["width"], 0.0, 0.0
+    side = (cfg.get("token_side") or {}).get("dim", 0)
+    for layer in cfg["layers"]:
+        a, r = layer["mixer"]["left"], layer["mixer"]["right"]
+        H, G, D, Dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+        mats = dm * (H * D + G * D + G * Dv) + H * Dv * dm + 2 * dm * side
+        attn = 2 * H * (D + Dv) * tokens * (tokens + 1) / 2
+        if layer["type"] == "parallel":
+            mats += dm * H * Dv                               # the gate
+            inner, gn = r["heads"] * r["vdim"], r["groups"] * r["state"]
+            mats += dm * (2 * inner + 2 * gn + r["heads"]) + inner * dm
+            scan = 4 * r["heads"] * r["state"] * r["vdim"] * tokens
+        else:
+            qk, vv = r["heads"] * r["dim"], r["heads"] * r["vdim"]
+            mats += dm * (2 * qk + 2 * vv) + vv * dm
+            scan = 4 * r["heads"] * r["dim"] * r["vdim"] * tokens
+        f = layer["mlp"]
+        if f is None:
+            up = up_run = 0
+        elif f["kind"] == "dense":
+            up = up_run = 3 * dm * f["ff"]
+        else:
+            ro = f["router"]
+            up = dm * ro["experts"] + 3 * dm * ro["top"] * f["expert"]["ff"]
+            up_run = dm * ro["experts"] + 3 * dm * ro["experts"] * f["expert"]["ff"]
+        asked += 2 * (mats + up) * tokens + attn + scan
+        run += 2 * (mats + up_run) * tokens + attn + scan
+    head = 2 * dm * cfg["vocab"]
+    return asked + head, run + head
+
+
 def qwen3_cfg(size, n_layers, vocab, max_positions):
     dm, nh, nkv, hd, ff = DESIGN_SIZES[size]
     return dict(QWEN3_4B, num_hidden_layers=n_layers, hidden_size=dm, num_attention_heads=nh,
@@ -574,6 +646,12 @@ def design_compare(args):
             designs = [("dunavik-attention", dunavik_cfg(size, n_layers, vocab, "attention", args.window))]
             designs += [(f"kefesun-{mx}", kefesun_cfg(size, n_layers, vocab, mx, args.window))
                         for mx in args.mixers.replace("latent", "mingru").split(",")]
+        if args.only == "munisun":
+            # beside Kefesun's mix of attention and recurrent layers: a recurrence with state per
+            # sequence, short convolutions, a routed feed-forward, float32 residual
+            designs = [("kefesun-mixed", kefesun_cfg(size, n_layers, vocab, "mixed", args.window))]
+            designs += [(f"munisun-{mx}", munisun_cfg(size, n_layers, vocab, mx))
+                        for mx in args.mixers.replace("attention", "parallel").replace("latent", "parallel2").split(",")]
         for design, cfg in designs:
             rng = np.random.default_rng(0)
             eng = Engine.open_random(cfg, seed=0, dtype=args.dtype, max_tokens=max(room * batch, T + 64),
@@ -582,6 +660,8 @@ def design_compare(args):
             flops_run = None
             if design.startswith("kefesun"):
                 flops, flops_run = kefesun_flops(cfg, T)
+            elif design.startswith("munisun"):
+                flops, flops_run = munisun_flops(cfg, T)
             else:
                 flops = (dunavik_flops(cfg, T, args.window) if design.startswith("dunavik")
                          else design_flops(design.split("-")[0], size, n_layers, T, vocab))
@@ -660,7 +740,7 @@ def main():
     ap.add_argument("--share", type=int, default=0,
                     help="--only zuzelorn: also a model whose layers share keys and values in groups of this many")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "prefill-timeline", "generate",
-                                                    "zuzelorn", "dunavik", "kefesun"],
+                                                    "zuzelorn", "dunavik", "kefesun", "munisun"],
                     help="run one part only and print its time (for profiling; no JSON line "
                          "but for generate); prefill-timeline: each kernel's share of one prefill "
                          "step; timeline: when each kernel of one replayed decode "
@@ -678,7 +758,7 @@ def main():
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
-    if args.only in ("zuzelorn", "dunavik", "kefesun"):
+    if args.only in ("zuzelorn", "dunavik", "kefesun", "munisun"):
         args.warmup = max(args.warmup, 3)
         return design_compare(args)
     full_layers = MODELS[args.model]["num_hidden_layers"]

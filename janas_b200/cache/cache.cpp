@@ -430,8 +430,13 @@ Json Cache::describe() const {
     }
     o.set("groups", gs);
     Json st = Json::array();
-    for (auto &kv : state_spec) st.push(kv.first);
+    Json sizes = Json::array();
+    for (auto &kv : state_spec) {
+        st.push(kv.first);
+        sizes.push((long long)kv.second.bytes());
+    }
     o.set("state_entries", st);
+    o.set("state_bytes", sizes);
     Json bst = Json::array();
     for (auto &kv : block_state_spec) bst.push(kv.first);
     o.set("block_state_entries", bst);
