@@ -86,7 +86,7 @@ MunisunConfig::Attention read_attention(const Json &m, const std::string &w) {
     return a;
 }
 
-Json attention_json(const MunisunConfig::Attention &a, bool parallel) {
+Json attention_json(const MunisunConfig::Attention &a) {
     Json m = Json::object();
     if (a.conv > 0) m.set("conv", a.conv);
     m.set("dim", a.dim);
@@ -107,7 +107,7 @@ Json attention_json(const MunisunConfig::Attention &a, bool parallel) {
         m.set("rot", r);
     }
     m.set("scale", a.scale);
-    if (parallel && a.softcap > 0) m.set("softcap", a.softcap);
+    if (a.softcap > 0) m.set("softcap", a.softcap);
     m.set("vdim", a.vdim);
     return m;
 }
@@ -238,7 +238,7 @@ Json MunisunConfig::to_json() const {
     Json ls = Json::array();
     for (auto &y : layers) {
         Json l = Json::object(), m = Json::object(), r = Json::object();
-        m.set("left", attention_json(y.left, y.type == "parallel"));
+        m.set("left", attention_json(y.left));
         if (y.type == "parallel") {
             r.set("conv", y.ssm_conv);
             r.set("groups", y.ssm_groups);
@@ -336,10 +336,10 @@ ModelSpec MunisunConfig::to_model_spec() const {
         left.params.set("v_head_dim", a.vdim);
         left.params.set("scale", a.scale);
         left.params.set("bias", false);
+        if (a.softcap > 0) left.params.set("softcap", a.softcap);
         if (parallel) {
             left.params.set("qk_norm_eps", norm_eps);
             left.params.set("gate", true);
-            if (a.softcap > 0) left.params.set("softcap", a.softcap);
         } else {
             left.params.set("qk_unit_norm_eps", norm_eps);
         }

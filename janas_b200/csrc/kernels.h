@@ -169,14 +169,17 @@ int jb_matrix_state_scan(const float *src, int S, long long stride, int ld, int 
                          int dt_ld, int dt_col0, const float *dt_bias, const float *a_log,
                          const float *skip, const float *decay, float *state, long long slot_stride,
                          const int32_t *row_seq, const int32_t *seq_slot, float *y, int n, int n_seqs,
-                         int H, int G, int N, int P, int every_row_starts, cudaStream_t st);
+                         int H, int G, int N, int P, int every_row_starts, float *scratch, int max_len,
+                         cudaStream_t st);
+int jb_matrix_state_piece(void);
+long long jb_matrix_state_scratch(int n_seqs, int max_len, int H, int N, int P);
 int jb_gated_part_norm(const float *y, const float *pre, int pre_S, long long pre_stride, int pre_ld,
                        int pre_col0, const float *post, int post_S, long long post_stride, int post_ld,
                        int post_col0, const float *w, float eps, void *out, int out_dt, int n, int width,
                        int parts, cudaStream_t st);
 int jb_pair_combine(const float *L, int SL, long long strideL, const float *R, int SR, long long strideR,
                     const float *wl, const float *wr, float sl, float sr, float eps, float *out, int n,
-                    int m, cudaStream_t st);
+                    int m, int few_rows, cudaStream_t st);
 int jb_token_gate(const float *P, int S, long long stride, int ld, const void *table, int table_dt,
                   int table_ld, int col0, const int32_t *tokens, void *out, int out_dt, int n, int dim,
                   cudaStream_t st);

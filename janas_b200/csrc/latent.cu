@@ -293,6 +293,8 @@ __global__ void activation_kernel(const float *__restrict__ z, int S, size_t str
     } else if (kind == JB_ACT_GELU_TANH) {
         float u = 0.7978845608028654f * fmaf(0.044715f * v * v, v, v);
         v = 0.5f * v * (1.0f + tanhf(u));
+    } else if (kind == JB_ACT_SILU) {
+        v = v / (1.0f + expf(-v));
     }
     out[i] = from_f<TO>(v);
 }
@@ -305,6 +307,8 @@ __device__ __forceinline__ float act_value(float v, int kind)
     }
     if (kind == JB_ACT_RELU)
         return fmaxf(v, 0.0f);
+    if (kind == JB_ACT_SILU)
+        return v / (1.0f + expf(-v));
     float u = 0.7978845608028654f * fmaf(0.044715f * v * v, v, v);
     return 0.5f * v * (1.0f + tanhf(u));
 }
@@ -524,7 +528,7 @@ extern "C" int jb_activation(const float *z, int S, long long stride, int ld, in
     size_t total = (size_t)n * ff;
     if (total == 0)
         return JB_OK;
-    if (S <= 0 || ff > ld || kind < 0 || kind > JB_ACT_GELU_TANH)
+    if (S <= 0 || ff > ld || kind < 0 || kind > JB_ACT_SILU)
         return JB_EINVAL;
     if (S == 1 && ff % 4 == 0 && ld % 4 == 0 && (uintptr_t)z % 16 == 0 && (uintptr_t)out % 16 == 0 &&
         (out_dt == JB_F32 || out_dt == JB_BF16)) {

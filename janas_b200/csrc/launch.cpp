@@ -243,16 +243,23 @@ Buf causal_conv(Device &d, const Stack &u, long long col0, long long C, const fl
 }
 
 Buf matrix_state_scan(Device &d, const Stack &src, const MatrixScan &m, float *state, long long slot_stride,
-                      const int32_t *row_seq, const int32_t *seq_slot, int n_seqs, bool every_row_starts) {
+                      const int32_t *row_seq, const int32_t *seq_slot, int n_seqs, bool every_row_starts,
+                      long long max_len) {
     if (!src || !state) fail(JB_LLM_EINVAL, "matrix_state_scan: no input or no state");
     if (m.dt && m.dt->n != src.n) fail(JB_LLM_EINVAL, "matrix_state_scan: the steps are of other rows");
     Buf y = d.pool.get(std::max<size_t>((size_t)src.n * (size_t)m.H * (size_t)m.P * 4, 16));
+    long long need = every_row_starts ? 0 : jb_matrix_state_scratch(n_seqs, (int)std::min<long long>(max_len, 0x7fffffff),
+                                                                     m.H, m.N, m.P);
+    Buf scratch;
+    if (need > 0) scratch = d.pool.get((size_t)need * 4);
     check(jb_matrix_state_scan(src.data(), src.S, src.stride(), as_int(src.m, "width"), (int)m.val_col0,
                                (int)m.key_col0, (int)m.qry_col0, m.silu ? 1 : 0, m.dt ? m.dt->data() : nullptr,
                                m.dt ? m.dt->S : 0, m.dt ? m.dt->stride() : 0, m.dt ? as_int(m.dt->m, "width") : 0,
                                (int)m.dt_col0, m.dt_bias, m.a_log, m.skip, m.decay, state, slot_stride, row_seq,
                                seq_slot, y.as<float>(), as_int(src.n, "rows"), n_seqs, m.H, m.G, m.N, m.P,
-                               every_row_starts ? 1 : 0, d.stream), "matrix_state_scan");
+                               every_row_starts ? 1 : 0, need > 0 ? scratch.as<float>() : nullptr,
+                               (int)std::min<long long>(max_len, 0x7fffffff), d.stream),
+          "matrix_state_scan", need > 0 ? 3 : 1);
     return y;
 }
 
@@ -271,7 +278,7 @@ Buf gated_part_norm(Device &d, const float *y, long long n, long long width, int
 }
 
 Stack pair_combine(Device &d, const Stack &L, const Stack &R, const float *wl, const float *wr, float sl,
-                   float sr, float eps) {
+                   float sr, float eps, bool few_rows) {
     if (!L || !R || L.n != R.n || L.m != R.m) fail(JB_LLM_EINVAL, "pair_combine: the two results differ in shape");
     if (L.bias || R.bias || L.skip || R.skip) fail(JB_LLM_EINVAL, "pair_combine: a result still has a term to be added");
     Stack out;
@@ -280,7 +287,7 @@ Stack pair_combine(Device &d, const Stack &L, const Stack &R, const float *wl, c
     out.m = L.m;
     out.buf = d.pool.get(std::max<size_t>((size_t)L.n * (size_t)L.m * 4, 16));
     check(jb_pair_combine(L.data(), L.S, L.stride(), R.data(), R.S, R.stride(), wl, wr, sl, sr, eps, out.data(),
-                          as_int(L.n, "rows"), as_int(L.m, "width"), d.stream), "pair_combine");
+                          as_int(L.n, "rows"), as_int(L.m, "width"), few_rows ? 1 : 0, d.stream), "pair_combine");
     return out;
 }
 

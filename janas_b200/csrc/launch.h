@@ -156,8 +156,11 @@ struct MatrixScan {
     const Stack *dt = nullptr;
     const float *dt_bias = nullptr, *a_log = nullptr, *skip = nullptr, *decay = nullptr;
 };
+// max_len: the most rows that one sequence brings (0: not known); long sequences are then cut
+// into pieces that run side by side, with a pass between them that carries the state along.
 Buf matrix_state_scan(Device &d, const Stack &src, const MatrixScan &m, float *state, long long slot_stride,
-                      const int32_t *row_seq, const int32_t *seq_slot, int n_seqs, bool every_row_starts);
+                      const int32_t *row_seq, const int32_t *seq_slot, int n_seqs, bool every_row_starts,
+                      long long max_len = 0);
 // rms(y * silu(pre)) in `parts` equal parts of the row, times w, times sigmoid(post): y float32
 // [n, width]; pre / post: sums whose columns from pre_col0 / post_col0 are read (null: none).
 Buf gated_part_norm(Device &d, const float *y, long long n, long long width, int parts, const Stack *pre,
@@ -165,8 +168,9 @@ Buf gated_part_norm(Device &d, const float *y, long long n, long long width, int
                     DType out_dt);
 // Two results as one stack of one sum: sl * sum(L) + sr * sum(R), or with weights (float32
 // [m] each) sl * rms(sum L) wl + sr * rms(sum R) wr.
+// few_rows: the bfloat16 path's kernel for a decode step's rows (a cluster of CTAs per row).
 Stack pair_combine(Device &d, const Stack &L, const Stack &R, const float *wl, const float *wr, float sl,
-                   float sr, float eps);
+                   float sr, float eps, bool few_rows = false);
 // gelu_tanh(sum P) * table[tokens[row], col0 .. col0 + dim - 1] as [n, dim] in out_dt
 Buf token_gate(Device &d, const Stack &P, const DevTensor &table, long long col0, long long dim,
                const int32_t *tokens, DType out_dt);

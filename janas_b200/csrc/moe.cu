@@ -195,26 +195,42 @@ activation_weighted_kernel(const float *__restrict__ z, int S, size_t stride, in
 
 // The same for experts with a gate: expert e's sums are [gate (ff) | up (ff)] in columns
 // 2 e ff .. of z, and out[r, e ff + j] = act(gate_j) * up_j * weights[r, e]; out: [n, n_experts ff].
-template <typename TO>
+// V values per thread (V = 4: ff a multiple of four and everything on 16-byte boundaries).
+template <typename TO, int V>
 __global__ void __launch_bounds__(256)
 gated_weighted_kernel(const float *__restrict__ z, int S, size_t stride, int ld,
                       const float *__restrict__ weights, int w_ld, int ff, int kind,
                       TO *__restrict__ out, int width)
 {
     pdl_trigger();
-    int r = blockIdx.x, c = (int)(blockIdx.y * blockDim.x + threadIdx.x);
+    int r = blockIdx.x, c = (int)(blockIdx.y * blockDim.x + threadIdx.x) * V;
     if (c >= width)
         return;
     pdl_wait();
     int e = c / ff, j = c - e * ff;
     float wgt = weights[(size_t)r * w_ld + e];
-    float v = 0.0f;
-    if (wgt != 0.0f) {
-        const float *src = z + (size_t)r * ld + (size_t)2 * e * ff + j;
-        float g = add_partials(0.0f, src, S, stride), u = add_partials(0.0f, src + ff, S, stride);
-        v = act_value(g, kind) * u * wgt;
+    const float *src = z + (size_t)r * ld + (size_t)2 * e * ff + j;
+    if (V == 4) {
+        float4 g = make_float4(0.0f, 0.0f, 0.0f, 0.0f), u = g;
+        if (wgt != 0.0f)
+            for (int sp = 0; sp < S; sp++) {
+                float4 a = load4(src + (size_t)sp * stride), b = load4(src + ff + (size_t)sp * stride);
+                g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+                u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+            }
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (wgt != 0.0f)
+            v = make_float4(act_value(g.x, kind) * u.x * wgt, act_value(g.y, kind) * u.y * wgt,
+                            act_value(g.z, kind) * u.z * wgt, act_value(g.w, kind) * u.w * wgt);
+        store4<TO>(out + (size_t)r * width + c, v);
+    } else {
+        float v = 0.0f;
+        if (wgt != 0.0f) {
+            float g = add_partials(0.0f, src, S, stride), u = add_partials(0.0f, src + ff, S, stride);
+            v = act_value(g, kind) * u * wgt;
+        }
+        out[(size_t)r * width + c] = from_f<TO>(v);
     }
-    out[(size_t)r * width + c] = from_f<TO>(v);
 }
 
 // y[r, c] += coef[r * coef_ld] * skip[r, c]: a part's own input handed on with a weight
@@ -316,14 +332,19 @@ extern "C" int jb_gated_weighted(const float *z, int S, long long stride, int ld
         S <= 0 || (kind != JB_ACT_RELU2 && kind != JB_ACT_RELU && kind != JB_ACT_GELU_TANH && kind != JB_ACT_SILU) ||
         (width + 255) / 256 > 65535)
         return JB_EINVAL;
-    dim3 grid((unsigned)n, (unsigned)((width + 255) / 256));
-    if (out_dt == JB_F32)
-        launch(gated_weighted_kernel<float>, grid, 256, 0, st, z, S, (size_t)stride, ld, weights, w_ld, ff, kind,
-               (float *)out, (int)width);
-    else if (out_dt == JB_BF16)
-        launch(gated_weighted_kernel<bf16>, grid, 256, 0, st, z, S, (size_t)stride, ld, weights, w_ld, ff, kind,
-               (bf16 *)out, (int)width);
-    else
+    bool vec = ff % 4 == 0 && ld % 4 == 0 && stride % 4 == 0 && (uintptr_t)z % 16 == 0 && (uintptr_t)out % 16 == 0;
+    long long per_row = vec ? width / 4 : width;
+    dim3 grid((unsigned)n, (unsigned)((per_row + 255) / 256));
+#define JB_GW(TO, V)                                                                                        \
+    launch(gated_weighted_kernel<TO, V>, grid, 256, 0, st, z, S, (size_t)stride, ld, weights, w_ld, ff, kind, \
+           (TO *)out, (int)width)
+    if (out_dt == JB_F32) {
+        if (vec) JB_GW(float, 4); else JB_GW(float, 1);
+    } else if (out_dt == JB_BF16) {
+        if (vec) JB_GW(bf16, 4); else JB_GW(bf16, 1);
+    } else {
         return JB_EINVAL;
+    }
+#undef JB_GW
     return launch_status();
 }

@@ -571,11 +571,13 @@ def matrix_state_scan(src: torch.Tensor, H: int, G: int, N: int, P: int, val_col
                       dt: Optional[torch.Tensor] = None, dt_col0: int = 0,
                       dt_bias: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None,
                       skip: Optional[torch.Tensor] = None, decay: Optional[torch.Tensor] = None,
-                      slot_stride: Optional[int] = None) -> torch.Tensor:
+                      slot_stride: Optional[int] = None, max_len: int = 0) -> torch.Tensor:
     """S_t = a_t S_{t-1} + b_t k_t v_t^T, y_t = S_t^T q_t + d v_t per head over the rows of each
     sequence; src [S, n, ld] holds v (H P columns), k and q (G N columns each).  With dt (sums
     with H columns from dt_col0): a = exp(-exp(a_log) softplus(dt + dt_bias)), b = the softplus,
-    d = skip; otherwise a = decay, b = 1, d = 0.  state: float32 [slots, H, N, P].  y: [n, H P]."""
+    d = skip; otherwise a = decay, b = 1, d = 0.  state: float32 [slots, H, N, P].  y: [n, H P].
+    max_len: the most rows one sequence brings; from twice ``jb_matrix_state_piece()`` rows on the
+    sequences are cut into pieces that run side by side."""
     src = stack(src)
     _need(src, "src", torch.float32, (None, None, None))
     S, n, ld = src.shape
@@ -586,10 +588,13 @@ def matrix_state_scan(src: torch.Tensor, H: int, G: int, N: int, P: int, val_col
         dS, dn, dld = dt.shape
     y = torch.empty((n, H * P), dtype=torch.float32, device=src.device)
     stride = slot_stride if slot_stride is not None else H * N * P
+    need = 0 if every_row_starts else lib().jb_matrix_state_scratch(n_seqs, max_len, H, N, P)
+    scratch = torch.empty((need,), dtype=torch.float32, device=src.device) if need > 0 else None
     _check(lib().jb_matrix_state_scan(_p(src), S, n * ld, ld, val_col0, key_col0, qry_col0, 1 if silu else 0,
                                       _p(dt), dS, dn * dld, dld, dt_col0, _p(dt_bias), _p(a_log), _p(skip),
                                       _p(decay), _p(state), stride, _p(row_seq), _p(seq_slot), _p(y), n, n_seqs,
-                                      H, G, N, P, 1 if every_row_starts else 0, _stream()), "matrix_state_scan")
+                                      H, G, N, P, 1 if every_row_starts else 0, _p(scratch), max_len, _stream()),
+           "matrix_state_scan", 3 if need > 0 else 1)
     return y
 
 
@@ -612,7 +617,7 @@ def gated_part_norm(y: torch.Tensor, parts: int, w: torch.Tensor, eps: float, ou
 
 
 def pair_combine(L: torch.Tensor, R: torch.Tensor, wl: Optional[torch.Tensor], wr: Optional[torch.Tensor],
-                 sl: float, sr: float, eps: float) -> torch.Tensor:
+                 sl: float, sr: float, eps: float, few_rows: bool = False) -> torch.Tensor:
     """sl * sum(L) + sr * sum(R), or with weights sl * rms(sum L) wl + sr * rms(sum R) wr."""
     L, R = stack(L), stack(R)
     _need(L, "L", torch.float32, (None, None, None))
@@ -620,7 +625,8 @@ def pair_combine(L: torch.Tensor, R: torch.Tensor, wl: Optional[torch.Tensor], w
     n, m = L.shape[1], L.shape[2]
     out = torch.empty((n, m), dtype=torch.float32, device=L.device)
     _check(lib().jb_pair_combine(_p(L), L.shape[0], n * m, _p(R), R.shape[0], n * m, _p(wl), _p(wr), float(sl),
-                                 float(sr), float(eps), _p(out), n, m, _stream()), "pair_combine")
+                                 float(sr), float(eps), _p(out), n, m, 1 if few_rows else 0, _stream()),
+           "pair_combine")
     return out
 
 

@@ -201,6 +201,98 @@ causal_conv_kernel(const float *__restrict__ u, int S, size_t stride, int ld, in
         st[(size_t)(pos % keep) * C + c] = cur;
 }
 
+// The same for one sum (S = 1), 2 to 4 taps and a multiple of four columns, with everything on
+// 16-byte boundaries: a thread has four columns of RB consecutive rows, keeps the last taps - 1
+// inputs in registers and moves along the rows (as short_conv_rows_kernel does).  The sums run
+// in the order of causal_conv_kernel, so a row's bits are the same on either way.
+template <typename TO, int TAPS, int RB>
+__global__ void __launch_bounds__(256)
+causal_conv_rows_kernel(const float *__restrict__ u, int ld, int col0, const float *__restrict__ w,
+                        const float *__restrict__ bias, float *__restrict__ state, size_t slot_stride,
+                        const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
+                        const int32_t *__restrict__ seq_slot, TO *__restrict__ out, int out_ld, int n, int C,
+                        int act, int what)
+{
+    constexpr int KEEP = TAPS - 1;
+    pdl_trigger();
+    int per_row = C / 4;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int rb = (int)(idx / per_row), c = (int)(idx - (size_t)rb * per_row) * 4;
+    int r0 = rb * RB, r1 = min(n, r0 + RB);
+    if (r0 >= n)
+        return;
+    float4 wt[TAPS];
+#pragma unroll
+    for (int j = 0; j < TAPS; j++)
+        wt[j] = make_float4(w[(size_t)c * TAPS + j], w[(size_t)(c + 1) * TAPS + j], w[(size_t)(c + 2) * TAPS + j],
+                            w[(size_t)(c + 3) * TAPS + j]);
+    float4 bs = bias != nullptr ? load4(bias + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    pdl_wait();
+    const float *in = u + col0 + c;
+    float4 hist[KEEP];          // hist[k - 1]: the input k positions back
+    int prev_seq = -1;
+    float4 in_rows[RB];
+    int in_pos[RB], in_seq[RB];
+#pragma unroll
+    for (int q = 0; q < RB; q++) {
+        int rr = min(r0 + q, r1 - 1);
+        in_rows[q] = load4(in + (size_t)rr * ld);
+        in_pos[q] = row_pos[rr];
+        in_seq[q] = row_seq[rr];
+    }
+#pragma unroll
+    for (int q = 0; q < RB; q++) {
+        int r = r0 + q;
+        if (r >= r1)
+            break;
+        int pos = in_pos[q], seq = in_seq[q];
+        float *st = state + (size_t)seq_slot[seq] * slot_stride;
+        if (r == r0 || seq != prev_seq) {
+#pragma unroll
+            for (int k = 1; k <= KEEP; k++) {
+                int p = pos - k;
+                if (p < 0)
+                    hist[k - 1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                else if (r - k >= 0 && row_seq[r - k] == seq)
+                    hist[k - 1] = load4(in + (size_t)(r - k) * ld);
+                else
+                    hist[k - 1] = load4(st + (size_t)(p % KEEP) * C + c);
+            }
+        }
+        prev_seq = seq;
+        float4 cur = in_rows[q];
+        if (what & 1) {
+            float4 acc = bs;
+            acc.x = fmaf(wt[KEEP].x, cur.x, acc.x);
+            acc.y = fmaf(wt[KEEP].y, cur.y, acc.y);
+            acc.z = fmaf(wt[KEEP].z, cur.z, acc.z);
+            acc.w = fmaf(wt[KEEP].w, cur.w, acc.w);
+#pragma unroll
+            for (int k = 1; k <= KEEP; k++) {
+                if (pos - k < 0)
+                    break;
+                acc.x = fmaf(wt[KEEP - k].x, hist[k - 1].x, acc.x);
+                acc.y = fmaf(wt[KEEP - k].y, hist[k - 1].y, acc.y);
+                acc.z = fmaf(wt[KEEP - k].z, hist[k - 1].z, acc.z);
+                acc.w = fmaf(wt[KEEP - k].w, hist[k - 1].w, acc.w);
+            }
+            if (act == 1) {
+                acc.x = acc.x / (1.0f + expf(-acc.x));
+                acc.y = acc.y / (1.0f + expf(-acc.y));
+                acc.z = acc.z / (1.0f + expf(-acc.z));
+                acc.w = acc.w / (1.0f + expf(-acc.w));
+            }
+            store4<TO>(out + (size_t)r * out_ld + c, acc);
+        }
+        if ((what & 2) && (r + KEEP >= n || row_seq[r + KEEP] != seq))
+            *reinterpret_cast<float4 *>(st + (size_t)(pos % KEEP) * C + c) = cur;
+#pragma unroll
+        for (int k = KEEP - 1; k >= 1; k--)
+            hist[k] = hist[k - 1];
+        hist[0] = cur;
+    }
+}
+
 // ---------------------------------------------------------------------- minGRU
 //
 //   z = sigmoid(P_z + b_z);  u = P_x + b_x;  c = u + 1/2 (u >= 0), sigmoid(u) (u < 0)
@@ -475,6 +567,34 @@ extern "C" int jb_causal_conv(const float *u, int S, long long stride, int ld, i
     if (taps < 1 || S <= 0 || ld < col0 + C || col0 < 0 || out_ld < C || u == nullptr || w == nullptr ||
         (taps > 1 && state == nullptr) || ((what & 1) && out == nullptr) || (act != 0 && act != 1))
         return JB_EINVAL;
+    auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    if (S == 1 && taps >= 2 && taps <= 4 && C % 4 == 0 && ld % 4 == 0 && col0 % 4 == 0 && out_ld % 4 == 0 &&
+        slot_stride % 4 == 0 && al16(u) && al16(bias) && al16(state) && al16(out)) {
+        // many rows: eight to a thread; few: one (a decode step's rows are all of other sequences)
+        bool many = (size_t)n * (C / 4) >= (size_t)8 * 148 * 1024;
+        int rbs = many ? 8 : 1;
+        size_t threads = (size_t)((n + rbs - 1) / rbs) * (C / 4);
+        unsigned g = (unsigned)((threads + 255) / 256);
+#define JB_CCR(TO, T, RB)                                                                                  \
+    launch(causal_conv_rows_kernel<TO, T, RB>, g, 256, 0, st, u, ld, col0, w, bias, state, (size_t)slot_stride, \
+           row_pos, row_seq, seq_slot, (TO *)out, out_ld, n, C, act, what)
+#define JB_CCR_T(TO, RB)                                                                                   \
+    do {                                                                                                   \
+        if (taps == 2) JB_CCR(TO, 2, RB);                                                                  \
+        else if (taps == 3) JB_CCR(TO, 3, RB);                                                             \
+        else JB_CCR(TO, 4, RB);                                                                            \
+    } while (0)
+        if (out_dt == JB_F32) {
+            if (many) JB_CCR_T(float, 8); else JB_CCR_T(float, 1);
+            return launch_status();
+        }
+        if (out_dt == JB_BF16) {
+            if (many) JB_CCR_T(bf16, 8); else JB_CCR_T(bf16, 1);
+            return launch_status();
+        }
+#undef JB_CCR_T
+#undef JB_CCR
+    }
     unsigned grid = (unsigned)(((size_t)n * C + 255) / 256);
     if (out_dt == JB_F32)
         launch(causal_conv_kernel<float>, grid, 256, 0, st, u, S, (size_t)stride, ld, col0, w, bias, state,

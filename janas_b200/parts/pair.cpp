@@ -112,7 +112,8 @@ public:
             ops::resolve_bias(*ctx.dev, result[i]);
         }
         return ops::pair_combine(*ctx.dev, result[0], result[1], normed_ ? (const float *)wl_.ptr : nullptr,
-                                 normed_ ? (const float *)wr_.ptr : nullptr, sl_, sr_, eps_);
+                                 normed_ ? (const float *)wr_.ptr : nullptr, sl_, sr_, eps_,
+                                 ctx.kind == DECODE && ctx.dtype == BF16);
     }
 
     Json info() const override {

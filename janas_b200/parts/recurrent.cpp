@@ -12,6 +12,8 @@
 // rounded to the compute type.  The state [W] lives in the cache per slot and is carried
 // from step to step, so prompts in portions, decoding and batches of unequal rows all
 // run the same kernels (csrc/recurrent.cu).
+#include <algorithm>
+
 #include "part.h"
 
 namespace jb {
@@ -90,6 +92,13 @@ private:
     std::string n_z_, n_x_, n_g_, n_o_, n_bias_;
     DevTensor w_in_, b_in_, w_o_;
 };
+
+// the most rows one sequence brings to the step (0 where the host does not know: a captured step)
+long long longest(const StepContext &ctx) {
+    long long m = 0;
+    for (long long v : ctx.seq_len) m = std::max(m, v);
+    return m;
+}
 
 // A selective state space mixer in Mamba-2's form (state-space duality): H heads of P values,
 // a state of N x P values per head, G groups of heads that share B and C.
@@ -203,7 +212,7 @@ public:
         m.a_log = (const float *)a_log_.ptr;
         m.skip = (const float *)d_.ptr;
         Buf y = ops::matrix_state_scan(d, xbc, m, st + conv_state(), stride, ctx.row_seq, ctx.seq_slot, ctx.n_seqs,
-                                       ctx.kind == DECODE);
+                                       ctx.kind == DECODE, longest(ctx));
         xbc = Stack();
         Buf a = ops::gated_part_norm(d, y.as<float>(), n, inner_, (int)parts_, &P, 0, nullptr, 0,
                                      (const float *)norm_.ptr, eps_, ctx.dtype);
@@ -310,8 +319,19 @@ public:
         m.val_col0 = 2 * H_ * D_;
         m.silu = true;
         m.decay = (const float *)decay_.ptr;
-        Buf y = ops::matrix_state_scan(d, P, m, (float *)cache.state, stride, ctx.row_seq, ctx.seq_slot, ctx.n_seqs,
-                                       ctx.kind == DECODE);
+        // Many rows: q, k and v are activated once, ahead of the recurrence, whose blocks would
+        // otherwise each activate the rows they read (several blocks read the same k and q).
+        Stack act;
+        if (ctx.kind != DECODE && n >= 64) {
+            act.buf = ops::activation(d, P, 2 * H_ * D_ + H_ * Dv_, ops::activation_kind("silu"), F32);
+            act.S = 1;
+            act.n = n;
+            act.m = 2 * H_ * D_ + H_ * Dv_;
+            m.silu = false;
+        }
+        Buf y = ops::matrix_state_scan(d, act ? act : P, m, (float *)cache.state, stride, ctx.row_seq, ctx.seq_slot,
+                                       ctx.n_seqs, ctx.kind == DECODE, longest(ctx));
+        act = Stack();
         Buf a = ops::gated_part_norm(d, y.as<float>(), n, H_ * Dv_, 1, nullptr, 0, &P, 2 * H_ * D_ + H_ * Dv_,
                                      (const float *)norm_.ptr, eps_, ctx.dtype);
         P = Stack();

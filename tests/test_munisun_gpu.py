@@ -59,7 +59,8 @@ def cuts(total, sizes):
 # ------------------------------------------------------------ mechanisms alone
 @pytest.mark.parametrize("taps,C,col0,ld,S,silu,bias", [(4, 40, 0, 40, 1, False, False), (3, 25, 7, 50, 2, True, True),
                                                         (2, 8, 8, 16, 1, False, True), (5, 130, 3, 140, 3, True, False),
-                                                        (1, 12, 0, 12, 1, True, True)])
+                                                        (1, 12, 0, 12, 1, True, True), (4, 64, 8, 80, 1, True, True),
+                                                        (3, 20, 4, 24, 1, False, False), (2, 128, 0, 128, 1, False, True)])
 def test_causal_convolution_and_its_state(taps, C, col0, ld, S, silu, bias):
     """Two sequences of unequal length in one step, then in portions down to one and two rows (shorter
     than the taps), in slots that are not in order: the last taps - 1 inputs pass through the state."""
@@ -98,6 +99,33 @@ def test_causal_convolution_and_its_state(taps, C, col0, ld, S, silu, bias):
         for i in range(2):
             close(torch.cat(got[i]), want[i], 2e-6, f"sizes {sizes} sequence {i}")
         assert float(state[0].abs().max()) == 0.0 and float(state[4].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("taps", [2, 3, 4])
+def test_causal_convolution_of_many_rows(taps):
+    """Enough rows for the kernel in which a thread moves along eight of them: two sequences that go on
+    from states an earlier step left, the border between them inside a thread's rows."""
+    C, lens, first = 2048, [1203, 1301], [5, 2]
+    u = [rnd(1, n, C + 8, seed=3 + i) for i, n in enumerate(lens)]
+    w, b = rnd(C, taps, scale=0.5, seed=1), rnd(C, seed=2)
+    want = [pm.silu(pm.causal_conv(x.sum(0)[:, 4:4 + C], w) + b) for x in u]
+    state = torch.zeros(3, taps - 1, C, device=DEV)
+    got = [[], []]
+    for rows in ([(0, f) for f in first], [(f, n - f) for f, n in zip(first, lens)]):
+        row_pos, row_seq = row_arrays(rows)
+        x = torch.cat([u[i][:, p0:p0 + cnt] for i, (p0, cnt) in enumerate(rows)], dim=1).contiguous().to(DEV)
+        args = (x, 4, C, w.to(DEV), b.to(DEV), state, row_pos.to(DEV), row_seq.to(DEV), i32([2, 0]), True, torch.float32)
+        if rows[0][0] == 0:
+            out = ops().causal_conv(*args)
+        else:
+            out = ops().causal_conv(*args, write_out=True, write_state=False)
+            ops().causal_conv(*args, write_out=False, write_state=True)
+        at = 0
+        for i, (p0, cnt) in enumerate(rows):
+            got[i].append(out[at:at + cnt].cpu())
+            at += cnt
+    for i in range(2):
+        close(torch.cat(got[i]), want[i], 2e-6, f"sequence {i}")
 
 
 def scan_inputs(kind, n, H, G, N, P, seed):
@@ -169,6 +197,40 @@ def test_matrix_state_recurrence(kind, H, G, N, P):
         assert float(state[1].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("kind,H,G,N,P", [("ssm", 2, 1, 16, 8), ("decay", 2, 2, 24, 20), ("ssm", 1, 1, 300, 4)])
+def test_long_sequences_in_pieces_side_by_side(kind, H, G, N, P):
+    """Sequences long enough to be cut into pieces that run side by side (one of them ends in the middle
+    of a piece, one is shorter than a piece), from states that an earlier step left."""
+    lens, slots = [40, 9, 3], [1, 3, 0]
+    more = [517, 384, 50]
+    params = {"dt_bias": rnd(H, seed=5) - 1.0, "a_log": rnd(H, scale=0.7, seed=6) - 0.5, "skip": 1 + rnd(H, scale=0.2, seed=7),
+              "decay": torch.tensor([0.97, 1.0][:H])}
+    data = [scan_inputs(kind, a + b, H, G, N, P, 30 + i) for i, (a, b) in enumerate(zip(lens, more))]
+    want = [plain_scan(kind, d[0], d[1], d[2], H, G, N, P, params) for d in data]
+    cols = data[0][1]
+    state = torch.zeros(4, H, N, P, device=DEV)
+    got = [[], [], []]
+    for rows in ([(0, n) for n in lens], [(n, m) for n, m in zip(lens, more)]):
+        _, row_seq = row_arrays(rows)
+        src = torch.cat([data[i][0][:, p0:p0 + cnt] for i, (p0, cnt) in enumerate(rows)], dim=1).contiguous().to(DEV)
+        if kind == "ssm":
+            kw = dict(dt=torch.cat([data[i][2][:, p0:p0 + cnt] for i, (p0, cnt) in enumerate(rows)], dim=1).contiguous().to(DEV),
+                      dt_col0=2, dt_bias=params["dt_bias"].to(DEV), a_log=params["a_log"].to(DEV), skip=params["skip"].to(DEV))
+        else:
+            kw = dict(decay=params["decay"].to(DEV), silu=True)
+        out = ops().matrix_state_scan(src, H, G, N, P, cols[0], cols[1], cols[2], state, row_seq.to(DEV), i32(slots), 3,
+                                      max_len=max(c for _, c in rows), **kw)
+        at = 0
+        for i, (p0, cnt) in enumerate(rows):
+            got[i].append(out[at:at + cnt].cpu())
+            at += cnt
+    assert ops().lib().jb_matrix_state_scratch(3, max(more), H, N, P) > 0
+    for i in range(3):
+        close(torch.cat(got[i]), want[i][0], 5e-5, f"{kind} sequence {i}")
+        close(state[slots[i]].cpu(), want[i][1], 5e-5, f"{kind} state {i}")
+    assert float(state[2].abs().max()) == 0.0
+
+
 def test_a_key_far_back_in_the_state():
     """A decay of exactly 1 keeps a key for good, a decay of 0.9 loses it: one key is written 700 tokens
     before the query that asks for it, among keys that are orthogonal to it."""
@@ -216,13 +278,15 @@ def test_gate_then_norm_in_parts(dtype, n, width, parts, pre, post):
     close(got, want, 3e-6 if dtype == torch.float32 else 1e-2)
 
 
-@pytest.mark.parametrize("n,m,SL,SR", [(1, 50, 1, 1), (9, 64, 2, 3), (130, 300, 1, 4)])
-def test_two_results_as_one(n, m, SL, SR):
+@pytest.mark.parametrize("n,m,SL,SR,few", [(1, 50, 1, 1, False), (9, 64, 2, 3, True), (130, 300, 1, 4, False),
+                                           (8, 2048, 3, 5, True), (1, 517, 1, 2, True), (32, 4100, 2, 2, True)])
+def test_two_results_as_one(n, m, SL, SR, few):
+    """few: the kernel for a decode step's rows (several blocks to a row)."""
     L, R = rnd(SL, n, m, seed=1), rnd(SR, n, m, scale=3.0, seed=2)
-    got = ops().pair_combine(L.to(DEV), R.to(DEV), None, None, 0.7, 1.1, 0.0).cpu()
+    got = ops().pair_combine(L.to(DEV), R.to(DEV), None, None, 0.7, 1.1, 0.0, few_rows=few).cpu()
     close(got, 0.7 * L.sum(0) + 1.1 * R.sum(0), 2e-6)
     wl, wr = 1 + rnd(m, scale=0.2, seed=3), 1 + rnd(m, scale=0.2, seed=4)
-    got = ops().pair_combine(L.to(DEV), R.to(DEV), wl.to(DEV), wr.to(DEV), 0.5, 0.5, 1e-5).cpu()
+    got = ops().pair_combine(L.to(DEV), R.to(DEV), wl.to(DEV), wr.to(DEV), 0.5, 0.5, 1e-5, few_rows=few).cpu()
     close(got, 0.5 * (pm.rms(L.sum(0), 1e-5) * wl + pm.rms(R.sum(0), 1e-5) * wr), 2e-6)
 
 

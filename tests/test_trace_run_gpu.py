@@ -181,3 +181,37 @@ def test_trace_run_kefesun(tmp_path, dtype, tol):
                 break                                   # a tie within rounding: stop comparing
             seq.append(int(lg.argmax()))
         assert len(seq) > 21 and " ".join(map(str, seq[20:])) in r.stdout, r.stdout[-500:]
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 3e-5), ("bfloat16", 5e-2)])
+def test_trace_run_munisun(tmp_path, dtype, tol):
+    """The same program on a model of the Munisun design: pages for the attention side, a state row per
+    request for the convolutions and the recurrences, a batch of unequal requests decoded together."""
+    import plain_munisun as pm
+    from munisun_models import model
+    folder, c, w = model("MD")
+    rng = np.random.default_rng(25)
+    v = c["vocab"]
+    batch = [(tokens(rng, 140, v), 131), (tokens(rng, 3, v), 1), (tokens(rng, 66, v), 64)]
+    steps = trace_batches([batch], want_prompt_all=False)
+    trace = tmp_path / "trace.jsonl"
+    write_trace(trace, steps)
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder,
+                        "--dtype", dtype, "--out", str(out), "--max-tokens", "209"],
+                       stdin=open(trace), capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert r.stdout.split("\n")[:len(steps)] == [f"done {s['step']}" for s in steps]
+    plain = [pm.forward(c, w, t, None if dtype == "float32" else "bfloat16").numpy() for t, _ in batch]
+    pos = {}
+    for st in steps:
+        n_want = sum(len(e["want"]) for e in st["entries"])
+        got = np.fromfile(out / f"{st['step']}.f32", dtype="<f4").reshape(n_want, v)
+        row = 0
+        for e in st["entries"]:
+            i = int(e["id"][3:])
+            base = pos.get(e["id"], 0)
+            for w_ in e["want"]:
+                assert rel_err(got[row], plain[i][base + w_]) <= tol, (st["step"], e["id"])
+                row += 1
+            pos[e["id"]] = base + len(e["tokens"])
