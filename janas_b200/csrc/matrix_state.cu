@@ -75,20 +75,24 @@ __device__ __forceinline__ int first_row_of(const int32_t *__restrict__ row_seq,
 //         local[z] and the product of its decays to decays[z, h] (no y).
 // MODE 2: a piece from the state in local[z] (what carry_kernel left there); y is written.
 // With pieces, blockIdx.z counts (sequence, piece); pieces that hold no row return.
+// NS: the split where it is fixed at compile time (0: nsplit_arg says it).
 // state: [H, N, P] per slot, slot_stride floats apart.  y: float32 [n, H P].
-template <int NR, int TB, int MODE>
+template <int NR, int TB, int MODE, int NS>
 __global__ void __launch_bounds__(128, NR <= 16 ? 5 : 3)
 matrix_state_scan_kernel(ScanIn in, float *__restrict__ state, size_t slot_stride,
                          const int32_t *__restrict__ row_seq, const int32_t *__restrict__ seq_slot,
                          float *__restrict__ y, float *__restrict__ local, float *__restrict__ decays, int n,
-                         int H, int G, int N, int P, int nsplit, int every_row_starts, int piece, int pieces)
+                         int H, int G, int N, int P, int nsplit_arg, int every_row_starts, int piece, int pieces)
 {
     extern __shared__ float4 sm4[];
     float *sm = reinterpret_cast<float *>(sm4);
     pdl_trigger();
+    // NS > 0: the split is known when the kernel is compiled and every lane has exactly NR rows
+    // (N = NR NS), so that the places in shared memory are constants and no row needs a check
+    const int nsplit = NS > 0 ? NS : nsplit_arg;
     const int PW = 32 / nsplit, PT = 4 * PW;
-    const int NP = (N + 4 * nsplit - 1) / (4 * nsplit) * (4 * nsplit);      // rows, padded with zeros
-    const int cnt4 = NP / (4 * nsplit);                                      // groups of four rows a lane
+    const int NP = NS > 0 ? NR * NS : (N + 4 * nsplit - 1) / (4 * nsplit) * (4 * nsplit);   // rows, padded with zeros
+    const int cnt4 = NS > 0 ? NR / 4 : NP / (4 * nsplit);                    // groups of four rows a lane
     int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int ns = lane / PW, pl = warp * PW + lane % PW;
     int p = blockIdx.x * PT + pl, h = blockIdx.y;
@@ -515,7 +519,9 @@ extern "C" int jb_matrix_state_scan(const float *src, int S, long long stride, i
         return JB_EINVAL;
     // 16 state values to a lane (more blocks, fewer registers, a shorter chain per row) where 32
     // lanes to a column are enough for that; 32 otherwise
-    bool small = N <= 16 * 32;
+    // (a decode step's one row per sequence moves the state and little else: fewer lanes to a
+    // column then, so that a warp reads 32 bytes of a state row at a time)
+    bool small = N <= 16 * 32 && !every_row_starts;
     int nsplit = scan_nsplit(N, P, small ? 16 : 32);
     if (((N + 4 * nsplit - 1) / (4 * nsplit)) * 4 > 32)
         return JB_EINVAL;
@@ -534,23 +540,28 @@ extern "C" int jb_matrix_state_scan(const float *src, int S, long long stride, i
     size_t per_head = (size_t)N * P;
     float *local = scratch, *decays = whole ? nullptr : scratch + (size_t)n_seqs * pieces * H * per_head;
     dim3 grid(ptiles, (unsigned)H, (unsigned)(n_seqs * pieces));
-#define JB_SCAN_N(NRV, MODE, SMEM)                                                                               \
+#define JB_SCAN_N(NRV, MODE, NSV, SMEM)                                                                        \
     do {                                                                                                       \
         if ((SMEM) > 48 * 1024) {                                                                              \
             /* long states: the rows in shared memory need more than a kernel gets unasked */                  \
-            static const bool asked = cudaFuncSetAttribute(matrix_state_scan_kernel<NRV, TB, MODE>,      \
+            static const bool asked = cudaFuncSetAttribute(matrix_state_scan_kernel<NRV, TB, MODE, NSV>,       \
                                                            cudaFuncAttributeMaxDynamicSharedMemorySize,        \
                                                            160 * 1024) == cudaSuccess;                         \
             (void)asked;                                                                                       \
         }                                                                                                      \
-        launch(matrix_state_scan_kernel<NRV, TB, MODE>, grid, 128, (SMEM), st, in, state,                \
+        launch(matrix_state_scan_kernel<NRV, TB, MODE, NSV>, grid, 128, (SMEM), st, in, state,                 \
                (size_t)slot_stride, row_seq, seq_slot, y, local, decays, n, H, G, N, P, nsplit,                \
                whole ? every_row_starts : 0, whole ? 0 : piece, pieces);                                       \
     } while (0)
-#define JB_SCAN(MODE, SMEM)                    \
-    do {                                       \
-        if (small) JB_SCAN_N(16, MODE, SMEM);  \
-        else JB_SCAN_N(32, MODE, SMEM);        \
+    // the commonest shapes have kernels of their own: 128 or 64 state rows, 16 to a lane (prompts),
+    // 128 rows, 32 to a lane (decode rows)
+#define JB_SCAN(MODE, SMEM)                                              \
+    do {                                                                 \
+        if (small && nsplit == 8 && N == 128) JB_SCAN_N(16, MODE, 8, SMEM); \
+        else if (small && nsplit == 4 && N == 64) JB_SCAN_N(16, MODE, 4, SMEM); \
+        else if (!small && nsplit == 4 && N == 128) JB_SCAN_N(32, MODE, 4, SMEM); \
+        else if (small) JB_SCAN_N(16, MODE, 0, SMEM);                    \
+        else JB_SCAN_N(32, MODE, 0, SMEM);                               \
     } while (0)
     if (whole) {
         JB_SCAN(0, smem);
