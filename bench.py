@@ -513,12 +513,12 @@ def munisun_cfg(size, n_layers, vocab, mixers="mixed"):
            "router": {"experts": 8, "groups": {"count": 4, "keep": 2}, "top": 2}}
     layers = []
     for i in range(n_layers):
-        left = {"dim": hd, "heads": nh, "kv_heads": nkv, "rot": {"base": 1000000.0, "dims": hd // 2},
+        left = {"dim": hd, "heads": nh, "kv_heads": nkv, "rot": {"base": 500000.0, "dims": hd // 2},
                 "scale": hd ** -0.5, "vdim": hd}
         mlp = moe if i % 2 else {"ff": ff, "kind": "dense"}
         if mixers == "parallel" or (mixers == "mixed" and i % 2 == 1):
             left["softcap"] = 50.0
-            left["rot"]["scaling"] = {"factor": 8.0, "high": 4.0, "low": 1.0, "original": 8192}
+            left["rot"]["scaling"] = {"factor": 16.0, "high": 8.0, "low": 2.0, "original": 8192}
             right = {"conv": 4, "groups": 8, "heads": dm // 64, "norm_groups": 8, "state": 128, "vdim": 64}
             layers.append({"type": "parallel", "mlp": mlp,
                            "mixer": {"left": left, "left_scale": 0.7, "right": right, "right_scale": 0.7}})

@@ -70,18 +70,18 @@ MA = config(64, 130, [par(attn(4, 2, 16, 24, 0.3, rot=(1000.0, 8), scaling=(4.0,
             side=8, eps=1e-6, scale=4.0)
 # multiples of nothing (the products leave the tensor cores); the linear attention first, two
 # taps, no rotation; a layer without a feed-forward; no cap, no stretching, one group, one norm
-# part, one tap (no state of the convolution), factors of exactly 1; one expert per token and no
-# groups; no token input
+# part, one tap on either side (no state of the convolution), factors of exactly 1; one expert per
+# token and no groups; no token input
 MB = config(50, 101, [par2(attn(3, 3, 10, 6, 0.4, conv=2), 2, 6, 10, [1.0, 0.7]),
                       par(attn(2, 1, 12, 10, 0.35, rot=(77.0, 4)), 3, 6, 5, 1, 1, 1, 1.0, 1.0, mlp=moe(3, 30, 1)),
-                      par2(attn(2, 2, 14, 14, 0.3, rot=(50.0, 6)), 1, 12, 12, [0.95], mlp=dense(70))],
+                      par2(attn(2, 2, 14, 14, 0.3, rot=(50.0, 6), conv=1), 1, 12, 12, [0.95], mlp=dense(70))],
             eps=1e-4, scale=1.0)
 # heads of 64 four to a key/value head and heads of 128 (the tensor cores take both in
 # bfloat16); four taps; a recurrence whose state is longer than a thread holds alone; every
 # group kept; a token input of sixteen values
 MC = config(128, 300, [par2(attn(4, 1, 64, 64, 0.11, rot=(100000.0, 32), conv=4), 2, 64, 64, [0.8, 0.999],
                             mlp=moe(8, 24, 3, groups=(4, 4))),
-                       par(attn(2, 2, 128, 128, 0.08, rot=(10000.0, 64), scaling=(8.0, 1.0, 4.0, 64), softcap=30.0),
+                       par(attn(2, 2, 128, 128, 0.08, rot=(10000.0, 64), scaling=(6.0, 1.0, 5.0, 64), softcap=30.0),
                            4, 32, 64, 1, 4, 4, 0.5, 1.5, mlp=dense(136)),
                        par2(attn(4, 1, 64, 64, 0.12, rot=(100000.0, 64), conv=4), 2, 64, 64, [0.9, 0.97],
                             mlp=moe(4, 72, 2, groups=(2, 1)))],

@@ -186,7 +186,8 @@ def test_trace_run_kefesun(tmp_path, dtype, tol):
 @pytest.mark.parametrize("dtype,tol", [("float32", 3e-5), ("bfloat16", 5e-2)])
 def test_trace_run_munisun(tmp_path, dtype, tol):
     """The same program on a model of the Munisun design: pages for the attention side, a state row per
-    request for the convolutions and the recurrences, a batch of unequal requests decoded together."""
+    request for the convolutions and the recurrences, a batch of unequal requests decoded together,
+    and the command line's generation on the same folder."""
     import plain_munisun as pm
     from munisun_models import model
     folder, c, w = model("MD")
@@ -215,3 +216,19 @@ def test_trace_run_munisun(tmp_path, dtype, tol):
                 assert rel_err(got[row], plain[i][base + w_]) <= tol, (st["step"], e["id"])
                 row += 1
             pos[e["id"]] = base + len(e["tokens"])
+    if dtype == "float32":
+        # greedy generation through the command line: the plain model's own choices
+        prompt = batch[2][0][:20]
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "janas-b200"), folder, "--tokens",
+                            " ".join(map(str, prompt)), "--max", "6", "--dtype", "float32"],
+                           capture_output=True, text=True, timeout=900)
+        assert r.returncode == 0, r.stderr[-2000:]
+        import torch
+        seq = list(prompt)
+        for _ in range(6):
+            lg = pm.forward(c, w, seq)[-1]
+            top = torch.topk(lg, 2).values
+            if (top[0] - top[1]) < 1e-4 * lg.abs().max():
+                break                                   # a tie within rounding: stop comparing
+            seq.append(int(lg.argmax()))
+        assert len(seq) > 21 and " ".join(map(str, seq[20:])) in r.stdout, r.stdout[-500:]
