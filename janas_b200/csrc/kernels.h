@@ -176,7 +176,7 @@ long long jb_matrix_state_scratch(int n_seqs, int max_len, int H, int N, int P);
 int jb_gated_part_norm(const float *y, const float *pre, int pre_S, long long pre_stride, int pre_ld,
                        int pre_col0, const float *post, int post_S, long long post_stride, int post_ld,
                        int post_col0, const float *w, float eps, void *out, int out_dt, int n, int width,
-                       int parts, cudaStream_t st);
+                       int parts, int few_rows, cudaStream_t st);
 int jb_pair_combine(const float *L, int SL, long long strideL, const float *R, int SR, long long strideR,
                     const float *wl, const float *wr, float sl, float sr, float eps, float *out, int n,
                     int m, int few_rows, cudaStream_t st);

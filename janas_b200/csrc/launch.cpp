@@ -265,7 +265,7 @@ Buf matrix_state_scan(Device &d, const Stack &src, const MatrixScan &m, float *s
 
 Buf gated_part_norm(Device &d, const float *y, long long n, long long width, int parts, const Stack *pre,
                     long long pre_col0, const Stack *post, long long post_col0, const float *w, float eps,
-                    DType out_dt) {
+                    DType out_dt, bool few_rows) {
     need_float(out_dt, "gated_part_norm output");
     if ((pre && pre->n != n) || (post && post->n != n)) fail(JB_LLM_EINVAL, "gated_part_norm: a gate of other rows");
     Buf out = d.pool.get(std::max<size_t>((size_t)n * (size_t)width * dtype_size(out_dt), 16));
@@ -273,7 +273,7 @@ Buf gated_part_norm(Device &d, const float *y, long long n, long long width, int
                              pre ? as_int(pre->m, "width") : 0, (int)pre_col0, post ? post->data() : nullptr,
                              post ? post->S : 0, post ? post->stride() : 0, post ? as_int(post->m, "width") : 0,
                              (int)post_col0, w, eps, out.ptr, out_dt, as_int(n, "rows"), as_int(width, "width"),
-                             parts, d.stream), "gated_part_norm");
+                             parts, few_rows ? 1 : 0, d.stream), "gated_part_norm");
     return out;
 }
 

@@ -163,9 +163,10 @@ Buf matrix_state_scan(Device &d, const Stack &src, const MatrixScan &m, float *s
                       long long max_len = 0);
 // rms(y * silu(pre)) in `parts` equal parts of the row, times w, times sigmoid(post): y float32
 // [n, width]; pre / post: sums whose columns from pre_col0 / post_col0 are read (null: none).
+// few_rows: the bfloat16 path's kernel for a decode step's rows (a cluster of CTAs per row and part).
 Buf gated_part_norm(Device &d, const float *y, long long n, long long width, int parts, const Stack *pre,
                     long long pre_col0, const Stack *post, long long post_col0, const float *w, float eps,
-                    DType out_dt);
+                    DType out_dt, bool few_rows = false);
 // Two results as one stack of one sum: sl * sum(L) + sr * sum(R), or with weights (float32
 // [m] each) sl * rms(sum L) wl + sr * rms(sum R) wr.
 // few_rows: the bfloat16 path's kernel for a decode step's rows (a cluster of CTAs per row).

@@ -359,6 +359,50 @@ gated_part_norm_kernel(const float *__restrict__ y, const float *__restrict__ pr
     }
 }
 
+// The same for few rows: a cluster of C CTAs per (row, part), each with `cols` columns of the part
+// held in shared memory; the CTAs exchange their sums of squares through one another's shared memory.
+template <typename TO, int C>
+__global__ void __launch_bounds__(256)
+gated_part_norm_cluster_kernel(const float *__restrict__ y, const float *__restrict__ pre, int pre_S,
+                               size_t pre_stride, int pre_ld, int pre_col0, const float *__restrict__ post,
+                               int post_S, size_t post_stride, int post_ld, int post_col0,
+                               const float *__restrict__ w, float eps, TO *__restrict__ out, int width, int parts,
+                               int cols)
+{
+    extern __shared__ float held[];
+    __shared__ float red[32];
+    __shared__ float part_sq[C];
+    pdl_trigger();
+    uint32_t rank = cluster_rank();
+    int idx = blockIdx.x / C, r = idx / parts, part = idx - r * parts, len = width / parts;
+    int c0 = part * len + (int)rank * cols, c1 = min(part * len + len, c0 + cols);
+    pdl_wait();
+    float ss = 0.0f;
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
+        float v = y[(size_t)r * width + c];
+        if (pre != nullptr)
+            v *= silu_f(add_partials(0.0f, pre + (size_t)r * pre_ld + pre_col0 + c, pre_S, pre_stride));
+        held[c - c0] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    if (threadIdx.x < C)
+        cluster_write(&part_sq[rank], threadIdx.x, ss);
+    cluster_arrive();
+    cluster_wait();
+    float tot = 0.0f;
+#pragma unroll
+    for (int k = 0; k < C; k++)
+        tot += part_sq[k];
+    float scale = 1.0f / sqrtf(tot / (float)len + eps);
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
+        float v = (held[c - c0] * scale) * w[c];
+        if (post != nullptr)
+            v *= sigmoid_f(add_partials(0.0f, post + (size_t)r * post_ld + post_col0 + c, post_S, post_stride));
+        out[(size_t)r * width + c] = from_f<TO>(v);
+    }
+}
+
 // Two mixers' results as one.  wl == null: out = sl * sum(L) + sr * sum(R).  Otherwise
 // out = sl * rms(sum L) wl + sr * rms(sum R) wr (each normed over the whole row).
 // A block per row; out: float32 [n, m].
@@ -580,7 +624,7 @@ extern "C" int jb_matrix_state_scan(const float *src, int S, long long stride, i
 extern "C" int jb_gated_part_norm(const float *y, const float *pre, int pre_S, long long pre_stride, int pre_ld,
                                   int pre_col0, const float *post, int post_S, long long post_stride, int post_ld,
                                   int post_col0, const float *w, float eps, void *out, int out_dt, int n, int width,
-                                  int parts, cudaStream_t st)
+                                  int parts, int few_rows, cudaStream_t st)
 {
     if (n <= 0)
         return JB_OK;
@@ -588,6 +632,17 @@ extern "C" int jb_gated_part_norm(const float *y, const float *pre, int pre_S, l
         (pre != nullptr && (pre_S <= 0 || pre_ld < pre_col0 + width)) ||
         (post != nullptr && (post_S <= 0 || post_ld < post_col0 + width)))
         return JB_EINVAL;
+    if (few_rows && n * parts <= 64 && width / parts >= 512 && out_dt == JB_BF16) {
+        // few blocks otherwise: a cluster of CTAs per (row, part)
+        constexpr int C = 4;
+        int cols = (width / parts + C - 1) / C;
+        if ((size_t)cols * 4 <= 40 * 1024) {
+            launch_cluster(gated_part_norm_cluster_kernel<bf16, C>, dim3((unsigned)(n * parts * C)), 256, (size_t)cols * 4,
+                           st, C, y, pre, pre_S, (size_t)pre_stride, pre_ld, pre_col0, post, post_S, (size_t)post_stride,
+                           post_ld, post_col0, w, eps, (bf16 *)out, width, parts, cols);
+            return launch_status();
+        }
+    }
     dim3 grid((unsigned)n, (unsigned)parts);
     size_t len = (size_t)(width / parts);
     int keep = len * 4 <= 40 * 1024 ? 1 : 0;

@@ -600,7 +600,7 @@ def matrix_state_scan(src: torch.Tensor, H: int, G: int, N: int, P: int, val_col
 
 def gated_part_norm(y: torch.Tensor, parts: int, w: torch.Tensor, eps: float, out_dtype: torch.dtype,
                     pre: Optional[torch.Tensor] = None, pre_col0: int = 0,
-                    post: Optional[torch.Tensor] = None, post_col0: int = 0) -> torch.Tensor:
+                    post: Optional[torch.Tensor] = None, post_col0: int = 0, few_rows: bool = False) -> torch.Tensor:
     """rms(y * silu(pre)) in ``parts`` equal parts of each row, times w, times sigmoid(post)."""
     _need(y, "y", torch.float32, (None, None))
     n, width = y.shape
@@ -612,7 +612,7 @@ def gated_part_norm(y: torch.Tensor, parts: int, w: torch.Tensor, eps: float, ou
     b = (0, 0, 0) if post is None else (post.shape[0], n * post.shape[2], post.shape[2])
     _check(lib().jb_gated_part_norm(_p(y), _p(pre), a[0], a[1], a[2], pre_col0, _p(post), b[0], b[1], b[2],
                                     post_col0, _p(w), float(eps), _p(out), _DT[out_dtype], n, width, parts,
-                                    _stream()), "gated_part_norm")
+                                    1 if few_rows else 0, _stream()), "gated_part_norm")
     return out
 
 

@@ -215,7 +215,7 @@ public:
                                        ctx.kind == DECODE, longest(ctx));
         xbc = Stack();
         Buf a = ops::gated_part_norm(d, y.as<float>(), n, inner_, (int)parts_, &P, 0, nullptr, 0,
-                                     (const float *)norm_.ptr, eps_, ctx.dtype);
+                                     (const float *)norm_.ptr, eps_, ctx.dtype, ctx.kind == DECODE && ctx.dtype == BF16);
         P = Stack();
         return ops::linear(d, a.ptr, ctx.dtype, n, inner_, w_o_);
     }
@@ -333,7 +333,7 @@ public:
                                        ctx.n_seqs, ctx.kind == DECODE, longest(ctx));
         act = Stack();
         Buf a = ops::gated_part_norm(d, y.as<float>(), n, H_ * Dv_, 1, nullptr, 0, &P, 2 * H_ * D_ + H_ * Dv_,
-                                     (const float *)norm_.ptr, eps_, ctx.dtype);
+                                     (const float *)norm_.ptr, eps_, ctx.dtype, ctx.kind == DECODE && ctx.dtype == BF16);
         P = Stack();
         return ops::linear(d, a.ptr, ctx.dtype, n, H_ * Dv_, w_o_);
     }

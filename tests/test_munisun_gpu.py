@@ -159,7 +159,8 @@ def plain_scan(kind, src, cols, dt, H, G, N, P, params, state=None):
 
 @pytest.mark.parametrize("kind,H,G,N,P", [("ssm", 4, 2, 8, 16), ("ssm", 3, 1, 5, 6), ("ssm", 2, 2, 40, 12), ("ssm", 4, 1, 64, 32),
                                           ("ssm", 1, 1, 130, 3), ("decay", 3, 3, 8, 24), ("decay", 2, 2, 64, 64),
-                                          ("decay", 1, 1, 12, 12), ("decay", 2, 2, 128, 40)])
+                                          ("decay", 1, 1, 12, 12), ("decay", 2, 2, 128, 40), ("ssm", 1, 1, 600, 2),
+                                          ("decay", 1, 1, 1024, 5)])
 def test_matrix_state_recurrence(kind, H, G, N, P):
     """Whole sequences against portions and token by token, two unequal sequences in slots that are
     not in order; the state is what the plain recurrence leaves."""
@@ -264,7 +265,8 @@ def test_a_key_far_back_in_the_state():
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n,width,parts,pre,post", [(5, 64, 2, True, False), (3, 72, 1, False, True), (70, 300, 4, True, True),
-                                                    (2, 50, 5, False, False), (9, 1024, 1, True, False)])
+                                                    (2, 50, 5, False, False), (9, 1024, 1, True, False), (2, 12000, 1, True, True), (8, 2560, 1, False, True),
+                                                    (8, 4096, 8, True, False), (3, 2052, 4, True, True)])
 def test_gate_then_norm_in_parts(dtype, n, width, parts, pre, post):
     y = rnd(n, width, scale=2.0, seed=1)
     z, g = rnd(2, n, width + 9, seed=2), rnd(3, n, width + 4, seed=3)
@@ -273,9 +275,10 @@ def test_gate_then_norm_in_parts(dtype, n, width, parts, pre, post):
     want = pm.rms(v.view(n, parts, width // parts), 1e-5).reshape(n, width) * w
     if post:
         want = want * torch.sigmoid(g.sum(0)[:, 4:4 + width])
-    got = ops().gated_part_norm(y.to(DEV), parts, w.to(DEV), 1e-5, dtype, pre=z.to(DEV) if pre else None, pre_col0=5,
-                                post=g.to(DEV) if post else None, post_col0=4).float().cpu()
-    close(got, want, 3e-6 if dtype == torch.float32 else 1e-2)
+    for few in (False, True):            # few: the kernel for a decode step's rows, where it takes the sizes
+        got = ops().gated_part_norm(y.to(DEV), parts, w.to(DEV), 1e-5, dtype, pre=z.to(DEV) if pre else None, pre_col0=5,
+                                    post=g.to(DEV) if post else None, post_col0=4, few_rows=few).float().cpu()
+        close(got, want, 3e-6 if dtype == torch.float32 else 1e-2)
 
 
 @pytest.mark.parametrize("n,m,SL,SR,few", [(1, 50, 1, 1, False), (9, 64, 2, 3, True), (130, 300, 1, 4, False),
