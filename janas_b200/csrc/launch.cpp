@@ -343,11 +343,11 @@ int activation_kind(const std::string &name) {
     return -1;
 }
 
-Buf activation(Device &d, const Stack &z, long long ff, int kind, DType out_dt) {
+Buf activation(Device &d, const Stack &z, long long ff, int kind, DType out_dt, long long col0) {
     need_float(out_dt, "activation output");
-    if (ff <= 0 || ff > z.m) fail(JB_LLM_EINVAL, "activation: the product is narrower than the feed-forward");
+    if (ff <= 0 || col0 < 0 || col0 + ff > z.m) fail(JB_LLM_EINVAL, "activation: the product is narrower than the feed-forward");
     Buf out = d.pool.get((size_t)z.n * (size_t)ff * dtype_size(out_dt));
-    check(jb_activation(z.data(), z.S, z.stride(), as_int(z.m, "width"), kind, out.ptr, out_dt,
+    check(jb_activation(z.data() + col0, z.S, z.stride(), as_int(z.m, "width"), kind, out.ptr, out_dt,
                         as_int(z.n, "rows"), as_int(ff, "width"), d.stream), "activation");
     return out;
 }

@@ -90,10 +90,10 @@ Buf layernorm(Device &d, float *x, long long n, long long dm, const LnParams &p,
 // x += mult * (sum a + sum b) (b may be null)
 void add_scaled_(Device &d, float *x, long long n, long long dm, const Stack &a, const Stack *b, float mult);
 
-// act(sum z) over the first ff columns of z's rows; kind: "relu2" (the square of
-// relu), "relu", "gelu_tanh".  [n, ff] in out_dt.
+// act(sum z) over ff columns of z's rows, from col0 on; kind: "relu2" (the square of
+// relu), "relu", "gelu_tanh", "silu".  [n, ff] in out_dt.
 int activation_kind(const std::string &name);       // -1: unknown
-Buf activation(Device &d, const Stack &z, long long ff, int kind, DType out_dt);
+Buf activation(Device &d, const Stack &z, long long ff, int kind, DType out_dt, long long col0 = 0);
 
 // x += norm(sum y + y.bias + y's skip term) w (+ b): a norm on a sublayer's result alone,
 // added to the residual stream in place.  rms: no mean is taken off.  few_rows: the

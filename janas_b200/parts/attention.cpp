@@ -384,7 +384,7 @@ public:
     }
 
     bool take_side_rows(DevTensor &m) override {
-        if (!w_in_ || m.shape.size() != 2 || m.shape[1] != hidden_ || side_cols_ > 0) return false;
+        if (!w_in_ || shared_ || m.shape.size() != 2 || m.shape[1] != hidden_ || side_cols_ > 0) return false;
         side_col0_ = w_in_.shape[0];
         side_cols_ = m.shape[0];
         std::vector<DevTensor> both = {w_in_, m};
@@ -417,7 +417,11 @@ public:
                                           "another layer's cache (cache_of in the run order)");
         long long n = ctx.n_rows;
         const float *b_in = bias_ ? (const float *)b_in_.ptr : nullptr;
-        Stack qkv = ops::linear(d, h, ctx.dtype, n, hidden_, w_in_);
+        // a pair's shared first product holds this mixer's columns first; it is borrowed, not owned
+        Stack own;
+        if (!shared_) own = ops::linear(d, h, ctx.dtype, n, hidden_, w_in_);
+        else if (!ctx.shared) fail(JB_LLM_EFAIL, "sink_attention: the shared first product is missing");
+        Stack &qkv = shared_ ? const_cast<Stack &>(*ctx.shared) : own;
         int max_chunks = (int)(ctx.max_pos / chunk_ + 1);
         if (g_.window) max_chunks = std::min(max_chunks, (g_.window - 1) / chunk_ + 2);
         // the kept first positions' chunks come in front of the window's
@@ -509,11 +513,18 @@ public:
 
     // the product goes to whoever gave the side rows, or back to the pool
     void keep_side(StepContext &ctx, Stack &qkv) {
+        if (shared_) return;            // the product is the pair's
         if (side_cols_ > 0) {
             ctx.side = std::move(qkv);
             ctx.side_col0 = side_col0_;
         }
         qkv = Stack();
+    }
+
+    DevTensor *first_matrix() override { return w_in_ && !bias_ && side_cols_ == 0 ? &w_in_ : nullptr; }
+    void share_first_product(long long col0) override {
+        if (col0 != 0) fail(JB_LLM_EINVAL, "sink_attention: its columns must come first in a shared product");
+        shared_ = true;
     }
 
     Stack output(StepContext &ctx, const Buf &a) {
@@ -539,6 +550,7 @@ private:
     bool qk_norm_ = false, score_bias_ = false;
     bool prepared_ = false;      // q and k are normed or rotated: qkv_prepare_append makes them
     bool gate_ = false, unit_norm_ = false;
+    bool shared_ = false;        // the first product's rows went into a pair's shared first product
     int conv_taps_ = 0;
     long long gate_col0_ = 0;
     std::string n_gate_, n_conv_;

@@ -8,9 +8,13 @@
 // cache group is that side's); the sides' fixed-size states lie one after the other in the
 // pair's state row per slot, and each side is told the row's length (LayerCache::state_stride).
 //
+// Where both sides offer the matrix of their first product (Mixer::first_matrix), the two are
+// one matrix and one product serves both sides (share_first_product false: each runs its own).
+//
 // params: hidden_size, left, right (parts), join ("sum" or "normed_mean"), left_scale and
-// right_scale (for "sum"; default 1), eps (for "normed_mean"), names (optional): left, right
-// (the sides' prefixes below the mixer's), left_out, right_out (the weights of "normed_mean")
+// right_scale (for "sum"; default 1), eps (for "normed_mean"), share_first_product (default
+// true), names (optional): left, right (the sides' prefixes below the mixer's), left_out,
+// right_out (the weights of "normed_mean")
 #include "part.h"
 
 namespace jb {
@@ -47,6 +51,7 @@ public:
         n_right_ = leaf("right", "right");
         n_left_out_ = leaf("left_out", "left.out");
         n_right_out_ = leaf("right_out", "right.out");
+        share_ = !s.has("share_first_product") || s.params.get("share_first_product").as_bool();
     }
 
     void tensors(const std::string &p, TensorList &out) const override {
@@ -65,10 +70,26 @@ public:
             wl_ = take(t, name(p, n_left_out_));
             wr_ = take(t, name(p, n_right_out_));
         }
+        // Both sides' first products read the same input: one product for both, the left side's
+        // columns first, the right side's from a multiple of eight on (rows of zeros between).
+        DevTensor *a = share_ ? left_->first_matrix() : nullptr, *b = share_ ? right_->first_matrix() : nullptr;
+        if (a && b && a->shape.size() == 2 && b->shape.size() == 2 && a->shape[1] == hidden_ && b->shape[1] == hidden_) {
+            long long rows = a->shape[0], col0 = (rows + 7) / 8 * 8;
+            std::vector<DevTensor> both = {*a};
+            if (col0 > rows) both.push_back(dev->tensor(a->dt, {col0 - rows, hidden_}, true));
+            both.push_back(*b);
+            long long total = col0 + b->shape[0];
+            if (total % 8) both.push_back(dev->tensor(a->dt, {8 - total % 8, hidden_}, true));    // rows of sums four to a load
+            *a = DevTensor();
+            *b = DevTensor();
+            w_first_ = fuse_rows(*dev, both);
+            left_->share_first_product(0);
+            right_->share_first_product(col0);
+        }
     }
 
     size_t weight_bytes() const override {
-        return left_->weight_bytes() + right_->weight_bytes() + wl_.bytes() + wr_.bytes();
+        return left_->weight_bytes() + right_->weight_bytes() + wl_.bytes() + wr_.bytes() + w_first_.bytes();
     }
 
     KVSpec kv_spec() const override { return left_->kv_spec().none() ? right_->kv_spec() : left_->kv_spec(); }
@@ -93,6 +114,11 @@ public:
             fail(JB_LLM_EINVAL, "pair: the cache holds no state of the two sides' size for the layer");
         long long stride = cache.state_stride > 0 ? cache.state_stride : total;
         long long at = 0;
+        Stack first;
+        if (w_first_) {
+            first = ops::linear(*ctx.dev, h, ctx.dtype, ctx.n_rows, hidden_, w_first_);
+            ctx.shared = &first;
+        }
         Stack result[2];
         Mixer *side[2] = {left_.get(), right_.get()};
         for (int i = 0; i < 2; i++) {
@@ -111,6 +137,8 @@ public:
             result[i] = side[i]->forward(ctx, h, lc);
             ops::resolve_bias(*ctx.dev, result[i]);
         }
+        ctx.shared = nullptr;
+        first = Stack();
         return ops::pair_combine(*ctx.dev, result[0], result[1], normed_ ? (const float *)wl_.ptr : nullptr,
                                  normed_ ? (const float *)wr_.ptr : nullptr, sl_, sr_, eps_,
                                  ctx.kind == DECODE && ctx.dtype == BF16);
@@ -130,6 +158,8 @@ private:
     float sl_ = 1.0f, sr_ = 1.0f, eps_ = 0.0f;
     std::string n_left_, n_right_, n_left_out_, n_right_out_;
     DevTensor wl_, wr_;
+    bool share_ = true;
+    DevTensor w_first_;          // both sides' first matrices as one, where both offer theirs
 };
 
 }  // namespace

@@ -95,6 +95,9 @@ struct StepContext {
     // it (Part::take_side_rows): their columns start at side_col0.
     Stack side;
     long long side_col0 = 0;
+    // The first product of two mixers that read the same input (a pair's sides), run once for both
+    // (Mixer::share_first_product says where each side's columns start); null: every mixer runs its own.
+    const Stack *shared = nullptr;
 };
 
 using TensorMap = std::map<std::string, DevTensor>;
@@ -179,6 +182,12 @@ public:
     virtual StateSpec state_spec() const { return StateSpec(); }
     // whether the mixer honours LayerCache::state_stride (it can then be one of a pair)
     virtual bool strided_state() const { return false; }
+    // The matrix of the mixer's first product over its input (after load()), or null where it has
+    // none to share.  An owner of two mixers over the same input may take both matrices into one
+    // and tell each mixer with share_first_product(col0) where its columns start in that product's
+    // sums; forward() then finds the sums in ctx.shared and runs no first product of its own.
+    virtual DevTensor *first_matrix() { return nullptr; }
+    virtual void share_first_product(long long col0) {}
     virtual void prepare(long long n_positions) {}
     // Whether the mixer can run a step of this kind.
     virtual bool supports(StepKind kind) const { return true; }

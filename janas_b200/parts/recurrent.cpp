@@ -174,6 +174,12 @@ public:
                d_.bytes() + norm_.bytes();
     }
 
+    DevTensor *first_matrix() override { return w_in_ ? &w_in_ : nullptr; }
+    void share_first_product(long long col0) override {
+        shared_ = true;
+        col0_ = col0;
+    }
+
     long long conv_state() const { return (long long)(taps_ - 1) * conv_; }
     StateSpec state_spec() const override { return StateSpec{{conv_state() + H_ * N_ * P_}, F32}; }
     bool strided_state() const override { return true; }
@@ -186,17 +192,21 @@ public:
         long long n = ctx.n_rows;
         long long stride = cache.state_stride > 0 ? cache.state_stride : state_spec().shape[0];
         float *st = (float *)cache.state;
-        Stack P = ops::linear(d, h, ctx.dtype, n, hidden_, w_in_);
+        Stack own;
+        if (!shared_) own = ops::linear(d, h, ctx.dtype, n, hidden_, w_in_);
+        else if (!ctx.shared) fail(JB_LLM_EFAIL, "mamba2: the shared first product is missing");
+        const Stack &P = shared_ ? *ctx.shared : own;
+        const long long c0 = shared_ ? col0_ : 0;
         // [x | B | C] through the convolution and silu, float32
         Stack xbc;
         xbc.S = 1;
         xbc.n = n;
         xbc.m = conv_;
         bool two = ctx.kind == EXTEND && taps_ > 1;
-        xbc.buf = ops::causal_conv(d, P, inner_, conv_, (const float *)conv_w_.ptr, (const float *)conv_b_.ptr, taps_,
+        xbc.buf = ops::causal_conv(d, P, c0 + inner_, conv_, (const float *)conv_w_.ptr, (const float *)conv_b_.ptr, taps_,
                                    st, stride, ctx.row_pos, ctx.row_seq, ctx.seq_slot, true, F32, true, !two);
         if (two)
-            ops::causal_conv(d, P, inner_, conv_, (const float *)conv_w_.ptr, (const float *)conv_b_.ptr, taps_, st,
+            ops::causal_conv(d, P, c0 + inner_, conv_, (const float *)conv_w_.ptr, (const float *)conv_b_.ptr, taps_, st,
                              stride, ctx.row_pos, ctx.row_seq, ctx.seq_slot, true, F32, false, true);
         ops::MatrixScan m;
         m.H = (int)H_;
@@ -207,16 +217,16 @@ public:
         m.key_col0 = inner_;
         m.qry_col0 = inner_ + G_ * N_;
         m.dt = &P;
-        m.dt_col0 = inner_ + conv_;
+        m.dt_col0 = c0 + inner_ + conv_;
         m.dt_bias = (const float *)dt_bias_.ptr;
         m.a_log = (const float *)a_log_.ptr;
         m.skip = (const float *)d_.ptr;
         Buf y = ops::matrix_state_scan(d, xbc, m, st + conv_state(), stride, ctx.row_seq, ctx.seq_slot, ctx.n_seqs,
                                        ctx.kind == DECODE, longest(ctx));
         xbc = Stack();
-        Buf a = ops::gated_part_norm(d, y.as<float>(), n, inner_, (int)parts_, &P, 0, nullptr, 0,
+        Buf a = ops::gated_part_norm(d, y.as<float>(), n, inner_, (int)parts_, &P, c0, nullptr, 0,
                                      (const float *)norm_.ptr, eps_, ctx.dtype, ctx.kind == DECODE && ctx.dtype == BF16);
-        P = Stack();
+        own = Stack();
         return ops::linear(d, a.ptr, ctx.dtype, n, inner_, w_o_);
     }
 
@@ -233,6 +243,8 @@ private:
     float eps_;
     std::string n_in_, n_conv_, n_conv_b_, n_dtb_, n_alog_, n_d_, n_norm_, n_o_;
     DevTensor w_in_, w_o_, conv_w_, conv_b_, dt_bias_, a_log_, d_, norm_;
+    bool shared_ = false;        // the in-product's rows went into a pair's shared first product
+    long long col0_ = 0;
 };
 
 // Linear attention with a fixed decay per head (lightning attention's recurrence): H heads,
@@ -298,6 +310,12 @@ public:
 
     size_t weight_bytes() const override { return w_in_.bytes() + w_o_.bytes() + norm_.bytes() + decay_.bytes(); }
 
+    DevTensor *first_matrix() override { return w_in_ ? &w_in_ : nullptr; }
+    void share_first_product(long long col0) override {
+        shared_ = true;
+        col0_ = col0;
+    }
+
     StateSpec state_spec() const override { return StateSpec{{H_ * D_ * Dv_}, F32}; }
     bool strided_state() const override { return true; }
     bool graph_safe() const override { return true; }
@@ -308,33 +326,40 @@ public:
             fail(JB_LLM_EINVAL, "decay_attention: the cache holds no state of this mixer's size for the layer");
         long long n = ctx.n_rows;
         long long stride = cache.state_stride > 0 ? cache.state_stride : state_spec().shape[0];
-        Stack P = ops::linear(d, h, ctx.dtype, n, hidden_, w_in_);
+        Stack own;
+        if (!shared_) own = ops::linear(d, h, ctx.dtype, n, hidden_, w_in_);
+        else if (!ctx.shared) fail(JB_LLM_EFAIL, "decay_attention: the shared first product is missing");
+        const Stack &P = shared_ ? *ctx.shared : own;
+        const long long c0 = shared_ ? col0_ : 0;
         ops::MatrixScan m;
         m.H = (int)H_;
         m.G = (int)H_;
         m.N = (int)D_;
         m.P = (int)Dv_;
-        m.qry_col0 = 0;
-        m.key_col0 = H_ * D_;
-        m.val_col0 = 2 * H_ * D_;
+        m.qry_col0 = c0;
+        m.key_col0 = c0 + H_ * D_;
+        m.val_col0 = c0 + 2 * H_ * D_;
         m.silu = true;
         m.decay = (const float *)decay_.ptr;
         // Many rows: q, k and v are activated once, ahead of the recurrence, whose blocks would
         // otherwise each activate the rows they read (several blocks read the same k and q).
         Stack act;
         if (ctx.kind != DECODE && n >= 64) {
-            act.buf = ops::activation(d, P, 2 * H_ * D_ + H_ * Dv_, ops::activation_kind("silu"), F32);
+            act.buf = ops::activation(d, P, 2 * H_ * D_ + H_ * Dv_, ops::activation_kind("silu"), F32, c0);
             act.S = 1;
             act.n = n;
             act.m = 2 * H_ * D_ + H_ * Dv_;
             m.silu = false;
+            m.qry_col0 = 0;
+            m.key_col0 = H_ * D_;
+            m.val_col0 = 2 * H_ * D_;
         }
         Buf y = ops::matrix_state_scan(d, act ? act : P, m, (float *)cache.state, stride, ctx.row_seq, ctx.seq_slot,
                                        ctx.n_seqs, ctx.kind == DECODE, longest(ctx));
         act = Stack();
-        Buf a = ops::gated_part_norm(d, y.as<float>(), n, H_ * Dv_, 1, nullptr, 0, &P, 2 * H_ * D_ + H_ * Dv_,
+        Buf a = ops::gated_part_norm(d, y.as<float>(), n, H_ * Dv_, 1, nullptr, 0, &P, c0 + 2 * H_ * D_ + H_ * Dv_,
                                      (const float *)norm_.ptr, eps_, ctx.dtype, ctx.kind == DECODE && ctx.dtype == BF16);
-        P = Stack();
+        own = Stack();
         return ops::linear(d, a.ptr, ctx.dtype, n, H_ * Dv_, w_o_);
     }
 
@@ -350,6 +375,8 @@ private:
     std::vector<float> decay_host_;
     std::string n_q_, n_k_, n_v_, n_g_, n_o_, n_norm_;
     DevTensor w_in_, w_o_, norm_, decay_;
+    bool shared_ = false;        // the [q | k | v | g] rows went into a pair's shared first product
+    long long col0_ = 0;
 };
 
 }  // namespace
