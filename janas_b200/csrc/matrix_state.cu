@@ -73,7 +73,8 @@ __device__ __forceinline__ int first_row_of(const int32_t *__restrict__ row_seq,
 // MODE 0: a sequence's rows of the step from the slot's state; y and the state are written.
 // MODE 1: a piece of `piece` rows from a state of zeros: the piece's own end state goes to
 //         local[z] and the product of its decays to decays[z, h] (no y).
-// MODE 2: a piece from the state in local[z] (what carry_kernel left there); y is written.
+// MODE 2: a piece from the state in local[z] (what carry_kernel left there); y is written, and
+//         by a sequence's last piece the slot's state.
 // With pieces, blockIdx.z counts (sequence, piece); pieces that hold no row return.
 // NS: the split where it is fixed at compile time (0: nsplit_arg says it).
 // state: [H, N, P] per slot, slot_stride floats apart.  y: float32 [n, H P].
@@ -108,9 +109,19 @@ matrix_state_scan_kernel(ScanIn in, float *__restrict__ state, size_t slot_strid
         r0 = first_row_of(row_seq, n, seq);
         r1 = first_row_of(row_seq, n, seq + 1);
     }
+    bool last_piece = true;
     if (MODE != 0) {
-        r0 += pc * piece;
-        r1 = min(r1, r0 + piece);
+        // A sequence that brings fewer than two pieces' rows stays whole (its first piece has
+        // all its rows), so that its sums are added in the order of the one-pass form: what
+        // else the step holds then does not change a sequence's bits.
+        int end = r1;
+        if (r1 - r0 >= 2 * piece) {
+            r0 += pc * piece;
+            r1 = min(r1, r0 + piece);
+        } else if (pc > 0) {
+            return;
+        }
+        last_piece = r1 == end;
     }
     if (r0 >= r1)
         return;
@@ -263,7 +274,11 @@ matrix_state_scan_kernel(ScanIn in, float *__restrict__ state, size_t slot_strid
             }
         }
     }
-    if (MODE != 2 && live) {
+    // MODE 2: a sequence's last piece has walked the state to its end in the order of the one-pass
+    // form; that is what the slot keeps (the carry pass's own end state differs from it in rounding)
+    if (MODE == 2)
+        st = state + (size_t)seq_slot[seq] * slot_stride + (size_t)h * N * P;
+    if ((MODE != 2 || last_piece) && live) {
 #pragma unroll
         for (int i = 0; i < NR; i++) {
             int nn = ((i >> 2) * nsplit + ns) * 4 + (i & 3);
@@ -276,8 +291,8 @@ matrix_state_scan_kernel(ScanIn in, float *__restrict__ state, size_t slot_strid
 }
 
 // Between the two passes over pieces: every sequence's state walks through its pieces,
-// S <- decays[z] S + local[z], and local[z] is left holding the state its piece starts from;
-// the state after the last piece goes back to the slot.  One thread per state value.
+// S <- decays[z] S + local[z], and local[z] is left holding the state its piece starts from
+// (the state after the last piece is written by the second pass).  One thread per state value.
 __global__ void __launch_bounds__(256)
 matrix_state_carry_kernel(float *__restrict__ state, size_t slot_stride, const int32_t *__restrict__ row_seq,
                           const int32_t *__restrict__ seq_slot, float *__restrict__ local,
@@ -292,7 +307,7 @@ matrix_state_carry_kernel(float *__restrict__ state, size_t slot_stride, const i
     int rows = first_row_of(row_seq, n, seq + 1) - first_row_of(row_seq, n, seq);
     if (rows <= 0)
         return;
-    int used = (rows + piece - 1) / piece;
+    int used = rows >= 2 * piece ? (rows + piece - 1) / piece : 1;
     float *st = state + (size_t)seq_slot[seq] * slot_stride + idx;
     pdl_wait();
     float S = *st;
@@ -313,7 +328,7 @@ matrix_state_carry_kernel(float *__restrict__ state, size_t slot_stride, const i
                 S = fmaf(dec[u], S, own[u]);
             }
     }
-    *st = S;
+    (void)S;         // the slot's state is written by the second pass's last piece
 }
 
 // out[r, c] = rms_part(y[r, :] * pre)[c] * w[c] * post, where pre = silu of the sums in

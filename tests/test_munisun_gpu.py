@@ -232,6 +232,42 @@ def test_long_sequences_in_pieces_side_by_side(kind, H, G, N, P):
     assert float(state[2].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("kind", ["ssm", "decay"])
+def test_a_sequences_bits_do_not_depend_on_the_batch(kind):
+    """A sequence of 200 rows alone (one pass) and beside one of 600 rows (pieces side by side): the
+    same bits, in y and in the state it leaves, also when it goes on from an earlier state."""
+    H, G, N, P = 2, 1 if kind == "ssm" else 2, 16, 8
+    params = {"dt_bias": rnd(H, seed=5) - 1.0, "a_log": rnd(H, scale=0.7, seed=6) - 0.5, "skip": 1 + rnd(H, scale=0.2, seed=7),
+              "decay": torch.tensor([0.97, 0.9])}
+    a, b = scan_inputs(kind, 205, H, G, N, P, 61), scan_inputs(kind, 600, H, G, N, P, 62)
+    cols = a[1]
+
+    def run(parts, state, slots, max_len):
+        rows = [(0, x[0].shape[1]) for x in parts]
+        _, row_seq = row_arrays(rows)
+        src = torch.cat([x[0] for x in parts], dim=1).contiguous().to(DEV)
+        if kind == "ssm":
+            kw = dict(dt=torch.cat([x[2] for x in parts], dim=1).contiguous().to(DEV), dt_col0=2,
+                      dt_bias=params["dt_bias"].to(DEV), a_log=params["a_log"].to(DEV), skip=params["skip"].to(DEV))
+        else:
+            kw = dict(decay=params["decay"].to(DEV), silu=True)
+        return ops().matrix_state_scan(src, H, G, N, P, cols[0], cols[1], cols[2], state, row_seq.to(DEV), i32(slots),
+                                       len(parts), max_len=max_len, **kw)
+
+    def cut(x, lo, hi):
+        return (x[0][:, lo:hi], x[1], None if x[2] is None else x[2][:, lo:hi])
+
+    for first in (0, 5):                 # from zero, and on from the state five rows left
+        alone, both = torch.zeros(2, H, N, P, device=DEV), torch.zeros(2, H, N, P, device=DEV)
+        if first:
+            run([cut(a, 0, first)], alone, [1], first)
+            run([cut(a, 0, first)], both, [1], first)
+        y1 = run([cut(a, first, 205)], alone, [1], 205 - first)
+        y2 = run([b, cut(a, first, 205)], both, [0, 1], 600)
+        assert torch.equal(y1, y2[600:])
+        assert torch.equal(alone[1], both[1])
+
+
 def test_a_key_far_back_in_the_state():
     """A decay of exactly 1 keeps a key for good, a decay of 0.9 loses it: one key is written 700 tokens
     before the query that asks for it, among keys that are orthogonal to it."""
