@@ -243,6 +243,34 @@ matrix_state_scan_kernel(ScanIn in, float *__restrict__ state, size_t slot_strid
         if (direct)
             copy_async_wait();
         __syncthreads();
+        if (MODE == 1) {
+            // The piece's own end state needs no row's state in between: over the batch's rows
+            // S <- (product of their decays) S + sum_s (b_s times the decays after s) k_s v_s^T,
+            // the rows taken last to first so that the decays after a row are a running product.
+            // One multiply-add a value and row instead of a multiply and a multiply-add.
+            float all = 1.0f;
+            for (int tt = 0; tt < tb; tt++)
+                all *= a_s[tt];
+            run *= all;
+#pragma unroll
+            for (int i = 0; i < NR; i++)
+                s[i] *= all;
+            float after = 1.0f;
+            for (int tt = tb - 1; tt >= 0; tt--) {
+                float wv = b_s[tt] * after * val_s[tt * PT + pl];
+                after *= a_s[tt];
+                const float4 *kk = reinterpret_cast<const float4 *>(key_s + tt * NP) + ns;
+#pragma unroll
+                for (int i4 = 0; i4 < NR / 4; i4++)
+                    if (i4 < cnt4) {
+                        float4 k4 = kk[i4 * nsplit];
+                        s[4 * i4 + 0] = fmaf(wv, k4.x, s[4 * i4 + 0]);
+                        s[4 * i4 + 1] = fmaf(wv, k4.y, s[4 * i4 + 1]);
+                        s[4 * i4 + 2] = fmaf(wv, k4.z, s[4 * i4 + 2]);
+                        s[4 * i4 + 3] = fmaf(wv, k4.w, s[4 * i4 + 3]);
+                    }
+            }
+        } else
         for (int tt = 0; tt < tb; tt++) {
             float a = a_s[tt], v = val_s[tt * PT + pl], bv = b_s[tt] * v;
             const float4 *kk = reinterpret_cast<const float4 *>(key_s + tt * NP) + ns;
